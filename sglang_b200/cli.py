@@ -1,4 +1,4 @@
-"""``python -m sglang_b200.cli {serve,generate,diffusion,bench-serving,router,killall,version}`` (reference ``python/sglang/cli/main.py:12-45``)."""
+"""``python -m sglang_b200.cli {serve,generate,trace-run,diffusion,bench-serving,router,killall,version}`` (reference ``python/sglang/cli/main.py:12-45``)."""
 from __future__ import annotations
 
 import json
@@ -28,6 +28,10 @@ def main(argv=None) -> None:
         eng = Engine(server_args=ServerArgs.from_cli_args(ns))
         out = eng.generate(ns.prompt, {"max_new_tokens": ns.max_new_tokens, "temperature": ns.temperature})
         print(json.dumps(out, indent=1))
+    elif cmd == "trace-run":                # scripted replay: dictated steps through the serving engine, logits out (entrypoints/trace_replay.py)
+        from .entrypoints.trace_replay import main as tr
+
+        sys.exit(tr(argv))
     elif cmd == "bench-serving":
         from .bench_serving import main as bs
 
@@ -59,7 +63,7 @@ def main(argv=None) -> None:
 
         print(__version__)
     else:
-        print("usage: python -m sglang_b200.cli {serve,generate,diffusion,bench-serving,router,killall,version} [args]")
+        print("usage: python -m sglang_b200.cli {serve,generate,trace-run,diffusion,bench-serving,router,killall,version} [args]")
 
 
 if __name__ == "__main__":

@@ -91,6 +91,9 @@ class ModelConfig:
     linear_attn: Optional[Dict[str, Any]] = None
     # state-space / hybrid decoders (models/mamba.py): num_heads, head_dim, d_state, d_conv, n_groups, norm_groups, chunk_size, pattern
     mamba: Optional[Dict[str, Any]] = None
+    # per-layer hybrid decoders (models/rirotar.py): {"layers": [{"type", "mixer": {...}, "mlp": {...} | None}, ...]} — every layer names its own
+    # mixer kind and sizes, so nothing about one layer is assumed of another
+    hybrid: Optional[Dict[str, Any]] = None
     # architectures without a native class: {"path", "arch"} -> models/transformers_fallback.py runs the Hugging Face module tree
     router_jitter_noise: Optional[float] = None      # Phi-3.5-MoE sparsemixer band
     hf_fallback: Optional[Dict[str, Any]] = None
@@ -353,6 +356,27 @@ _ARCH_DEFAULTS = {"GPT2LMHeadModel": dict(pos_emb="learned", tie_word_embeddings
                   "Qwen3ForCausalLM": dict(qk_norm=True), "Qwen3MoeForCausalLM": dict(qk_norm=True)}
 
 
+def rirotar_config(hf: Dict[str, Any]) -> Dict[str, Any]:
+    """Rirotar ``config.json`` -> ModelConfig fields.  The file lists the layers one by one (``layers[i]`` = ``type`` of the mixer, its sizes
+    under ``mixer``, the feed-forward under ``mlp`` or null); the global keys are ``width``, ``vocab``, ``norm.eps`` and ``logit_softcap``.
+    The flat fields below are only summaries for code that sizes buffers (largest head count, largest feed-forward); the model reads
+    ``hybrid["layers"]``."""
+    layers = [dict(l) for l in hf["layers"]]
+    width = int(hf["width"])
+    ffs = [int(l["mlp"]["ff"]) if l["mlp"]["kind"] == "dense" else int(l["mlp"]["expert"]["ff"]) * int(l["mlp"]["router"]["top"])
+           for l in layers if l.get("mlp")]
+    experts = [int(l["mlp"]["router"]["experts"]) for l in layers if l.get("mlp") and l["mlp"]["kind"] == "moe"]
+    heads = max([int(l["mixer"]["heads"]) for l in layers] or [1])
+    return dict(architecture="Rirotar", hidden_size=width, vocab_size=int(hf["vocab"]), num_hidden_layers=len(layers),
+                rms_norm_eps=float((hf.get("norm") or {}).get("eps", 1e-6)), final_logit_softcapping=float(hf.get("logit_softcap") or 0.0),
+                num_attention_heads=heads, num_key_value_heads=1, head_dim=max([int(l["mixer"]["dim"]) for l in layers] or [width // heads]),
+                intermediate_size=max(ffs or [width]), num_local_experts=max(experts or [0]),
+                num_experts_per_tok=max([int(l["mlp"]["router"]["top"]) for l in layers if l.get("mlp") and l["mlp"]["kind"] == "moe"] or [0]),
+                max_position_embeddings=int(hf.get("max_positions") or (1 << 20)), tie_word_embeddings=False, eos_token_id=None,
+                dtype={"float16": "float16", "float32": "float32"}.get(hf.get("dtype") or "bfloat16", "bfloat16"),
+                hybrid={"layers": layers})
+
+
 def _has_native_class(arch: str) -> bool:
     from ..models.registry import supported_architectures
 
@@ -398,6 +422,14 @@ def load_model_config(model_path: str, overrides: Optional[Dict[str, Any]] = Non
                 raise FileNotFoundError(f"{cfg_file} not found (offline box: use dummy:<preset>, a local HF directory or a .gguf file)")
             with open(cfg_file) as f:
                 hf = json.load(f)
+        if hf.get("architecture") == "Rirotar":
+            kw = rirotar_config(hf)
+            kw["name"] = os.path.basename(model_path.rstrip("/"))
+            kw.update(overrides)
+            cfg = ModelConfig(**kw)
+            if context_length is not None and context_length > 0:
+                cfg.max_position_embeddings = min(cfg.max_position_embeddings, context_length)
+            return cfg
         text = hf.get("text_config", hf)
         fields = {f.name for f in dataclasses.fields(ModelConfig)}
         text = {_HF_KEY_MAP.get(k, k): v for k, v in text.items()}

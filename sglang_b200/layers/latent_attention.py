@@ -1,0 +1,90 @@
+"""Latent (low-rank KV) attention without positional rotation, with a sliding window and per-head soft-max sinks.
+
+Every token caches ONE latent row ``c = rmsnorm(W_dkv h)`` of ``kv_rank`` numbers; keys and values of all heads are linear maps of it
+(``k_h = W_uk,h c``, ``v_h = W_uv,h c``).  Attention runs in the absorbed form, like the framework's other latent-attention family
+(``models/deepseek.py``): the key up-projection moves to the query side and the value up-projection behind the soft-max,
+
+    q~_h = W_uk,h^T q_h                      [kv_rank]
+    p_hij = softmax_j(scale * q~_hi . c_j)   over the window  0 <= i - j < window, with exp(sink_h) added to the denominator
+    o_hi  = W_uv,h (sum_j p_hij c_j)
+
+so the paged cache holds ``kv_rank`` values per token and layer and the kernel is multi-query attention over the latent rows
+(``ops.latent_attention``, csrc/kernels/latent_attention.cu: one kernel for prompt portions and single decode tokens).  The soft-max, the
+latent norm and both absorbed products are fp32; the cache is in the model dtype.
+
+The window only masks: pages of tokens that left the window are still held until the request ends (the pool is sized by live tokens).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+from torch import nn
+
+from .. import ops
+from ..model_executor.forward_batch import ForwardBatch
+
+
+class LatentCacheSpec:
+    """what the model runner reads to size the paged pool: one "KV head" of ``cache_width`` per token, a single plane (values are a view)"""
+
+    def __init__(self, num_heads: int, cache_width: int, layer_id: int, scale: float, window: int):
+        self.num_heads, self.num_kv_heads, self.head_dim, self.kv_head_dim = num_heads, 1, cache_width, cache_width
+        self.latent_v_dim = cache_width
+        self.layer_id, self.scale, self.window, self.logit_cap, self.rope, self.sinks = layer_id, scale, window, 0.0, None, None
+
+
+class WindowedLatentAttention(nn.Module):
+    def __init__(self, width: int, heads: int, dim: int, vdim: int, kv_rank: int, scale: Optional[float], window: int, eps: float, layer_id: int,
+                 dtype, cache_width: Optional[int] = None, sinks: bool = True):
+        super().__init__()
+        self.H, self.D, self.Dv, self.R = heads, dim, vdim, kv_rank
+        self.eps = eps
+        mk = lambda *s: nn.Parameter(torch.zeros(*s, dtype=dtype), requires_grad=False)
+        self.qc_weight = mk(heads * dim + kv_rank, width)          # rows [q (heads x dim) | latent down-projection (kv_rank)]: one GEMM
+        self.latent_norm = nn.Parameter(torch.ones(kv_rank, dtype=dtype), requires_grad=False)
+        self.uk = mk(heads * dim, kv_rank)
+        self.uv = mk(heads * vdim, kv_rank)
+        self.o_weight = mk(width, heads * vdim)
+        self.sinks = nn.Parameter(torch.zeros(heads, dtype=torch.float32), requires_grad=False) if sinks else None
+        self.attn = LatentCacheSpec(heads, cache_width or kv_rank, layer_id, float(scale) if scale is not None else dim ** -0.5, int(window or -1))
+        self._uk32 = self._uv32 = None
+
+    def load(self, leaf: str, w: torch.Tensor) -> bool:
+        hd = self.H * self.D
+        if leaf == "q":
+            self.qc_weight.data[:hd].copy_(w)
+        elif leaf == "dkv":
+            self.qc_weight.data[hd:].copy_(w)
+        elif leaf == "dkv.norm":
+            self.latent_norm.data.copy_(w)
+        elif leaf in ("uk", "uv"):
+            getattr(self, leaf).data.copy_(w)
+            self._uk32 = self._uv32 = None
+        elif leaf == "sink":
+            self.sinks.data.copy_(w.float())
+        elif leaf == "o":
+            self.o_weight.data.copy_(w)
+        else:
+            return False
+        return True
+
+    def _absorbed(self):
+        if self._uk32 is None or self._uk32.device != self.uk.device:
+            self._uk32 = self.uk.detach().float().view(self.H, self.D, self.R).contiguous()                   # [H, D, R]
+            self._uv32 = self.uv.detach().float().view(self.H, self.Dv, self.R).transpose(1, 2).contiguous()  # [H, R, Dv]
+        return self._uk32, self._uv32
+
+    def forward(self, h: torch.Tensor, fb: ForwardBatch) -> torch.Tensor:
+        T = h.shape[0]
+        hd = self.H * self.D
+        qc = ops.linear(h, self.qc_weight)
+        c = ops.rmsnorm(qc[:, hd:].contiguous(), self.latent_norm, self.eps)
+        cache = fb.kv_pool.k(self.attn.layer_id)                          # [slots, 1, cache_width]
+        cache[fb.out_cache_loc.long(), 0, : self.R] = c.to(cache.dtype)
+        uk, uv = self._absorbed()
+        q_lat = torch.bmm(qc[:, :hd].float().view(T, self.H, self.D).transpose(0, 1), uk).transpose(0, 1).contiguous()      # [T, H, R]
+        o_lat = ops.latent_attention(q_lat, cache, self.R, fb.page_table, fb.req_slots, fb.seq_lens, fb.cu_q, fb.q_lens, fb.max_q_len, fb.page_size,
+                                     self.attn.scale, self.attn.window, self.sinks)
+        o = torch.bmm(o_lat.transpose(0, 1), uv).transpose(0, 1).reshape(T, self.H * self.Dv)
+        return ops.linear(o.to(h.dtype), self.o_weight)

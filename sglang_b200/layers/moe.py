@@ -31,6 +31,26 @@ def select_experts(router_logits: torch.Tensor, top_k: int, renormalize: bool = 
     return moe_ops.topk_softmax(router_logits, top_k, renormalize)
 
 
+def grouped_sigmoid_route(logits: torch.Tensor, top_k: int, n_groups: int = 1, keep_groups: int = 1, scale: float = 1.0,
+                          group_top: int = 2) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Sigmoid router with group-limited choice, fp32: scores ``s = sigmoid(logits)``; the experts form ``n_groups`` equal groups of
+    neighbours, a group scores the sum of its ``group_top`` largest ``s``, and only experts of the ``keep_groups`` best groups can be
+    chosen; the ``top_k`` largest allowed ``s`` win and are weighted ``s / (sum of the chosen s + 1e-20) * scale``.
+    -> (weights fp32 [T, top_k], expert ids int32 [T, top_k])"""
+    s = torch.sigmoid(logits.float())
+    T, E = s.shape
+    choice = s
+    if n_groups > 1 and keep_groups < n_groups:
+        per = E // n_groups
+        gs = s.view(T, n_groups, per).topk(min(group_top, per), dim=-1).values.sum(-1)
+        keep = torch.zeros_like(gs, dtype=torch.bool).scatter_(1, gs.topk(keep_groups, dim=-1).indices, True)
+        choice = s.masked_fill(~keep[:, :, None].expand(T, n_groups, per).reshape(T, E), -1.0)
+    ids = choice.topk(top_k, dim=-1).indices
+    w = s.gather(1, ids)
+    w = w / (w.sum(-1, keepdim=True) + 1e-20) * scale
+    return w.contiguous(), ids.to(torch.int32).contiguous()
+
+
 class FusedMoE(nn.Module):
     def __init__(self, num_experts: int, top_k: int, hidden_size: int, intermediate_size: int, dtype=torch.bfloat16,
                  renormalize: bool = True, ep_size: int = 1, quant=None, layer_id: int = 0):
@@ -52,6 +72,7 @@ class FusedMoE(nn.Module):
         self.inter_local = intermediate_size // self.moe_tp
         self.w13 = nn.Parameter(torch.zeros(self.local_experts, 2 * self.inter_local, hidden_size, dtype=dtype), requires_grad=False)
         self.w2 = nn.Parameter(torch.zeros(self.local_experts, hidden_size, self.inter_local, dtype=dtype), requires_grad=False)
+        self.act = None          # None = silu(gate) * up; else a callable on the [rows, 2I] gate|up block (clamped GLU: models/rirotar.py)
         self.expert_load = None  # EPLB recorder hook
         self.placement = None    # eplb/placement.py ExpertPlacement once experts are replicated / moved; None = contiguous default
         self.rep_table = self.rep_count = None
@@ -160,7 +181,7 @@ class FusedMoE(nn.Module):
                 # combine kernel pushes the partial sums to every peer; the next RMSNorm reduces them locally
                 off = tp.nvl.moe_push(x, self.w13, self.w2, w, ids.to(torch.int32), self.expert_offset)
                 return PendingAllReduce(tp.nvl, off, x.shape[0], x.shape[1], "push")
-        y = moe_ops.fused_moe(x, self.w13, self.w2, w, ids, self.expert_offset)
+        y = moe_ops.fused_moe(x, self.w13, self.w2, w, ids, self.expert_offset, self.act)
         if tp.world_size > 1:
             y = tp.all_reduce(y)
         return y

@@ -238,6 +238,7 @@ class ScheduleBatch:
     sample_mask: Optional[np.ndarray] = None
     mm_embeds: Any = None
     decoding_reqs: Optional[List[Req]] = None      # mixed mode
+    logit_rows: Optional[np.ndarray] = None        # rows of this step's token batch whose full logits the result carries (trace replay)
 
     def batch_size(self) -> int:
         return len(self.reqs)

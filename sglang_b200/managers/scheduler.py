@@ -564,6 +564,61 @@ class Scheduler:
         self.decode_ct += 1
         return snap
 
+    # ================================================================== scripted replay (entrypoints/trace_replay.py)
+    def replay_step(self, entries: List[Tuple[str, List[int], List[int]]], end: List[str]) -> Optional[np.ndarray]:
+        """Run ONE step whose contents are dictated from outside instead of chosen by the policy: ``entries`` = (request id, its next
+        tokens, which of them need full logits).  An unknown id is admitted (slot + pages through the KV manager); all entries form one
+        batch — a decode batch when every entry is a single token of a request that already holds tokens, else a ragged extend batch in
+        which running requests ride as one-token extends, exactly what mixed chunked prefill builds.  Nothing is sampled into the requests:
+        the tokens are the script's.  ``end`` releases requests after the step.  Returns the asked rows' logits fp32 [rows, vocab]."""
+        live = self.__dict__.setdefault("_replay_reqs", {})
+        reqs, rows, off = [], [], 0
+        for rid, toks, want in entries:
+            r = live.get(rid)
+            if r is None:
+                r = Req(rid, [], SamplingParams(max_new_tokens=1 << 30, temperature=0.0, ignore_eos=True))
+                if not self.kv.admit(r):
+                    raise RuntimeError(f"replay: no free request slot for {rid!r} ({self.max_running} slots)")
+                live[rid] = r
+            r.origin_input_ids.extend(int(t) for t in toks)
+            reqs.append(r)
+            rows.extend(off + int(w) for w in want)
+            off += len(toks)
+        out = None
+        if reqs:
+            decode = all(len(t) == 1 and r.kv_len > 0 for r, (_, t, _) in zip(reqs, entries))
+            if decode:
+                batch = ScheduleBatch(reqs=reqs, forward_mode=ForwardMode.DECODE)
+                batch.init_decode_state()
+                positions = batch.seq_lens.copy()
+                loc = self.kv.alloc_for_decode(reqs, batch.req_slots, positions)
+                if loc is None:
+                    raise RuntimeError("replay: out of KV pages")
+                batch.positions, batch.out_cache_loc = positions.astype(np.int32), loc
+                batch.seq_lens = batch.seq_lens + 1
+                batch.pt_rows, batch.pt_cols, batch.pt_vals = self.kv.take_deltas()
+                for r in reqs:
+                    r.kv_len += 1
+                # the decode path reads each request's input token from the device-side token buffer (where sampling leaves it)
+                self.worker.set_next_tokens(batch.req_slots, np.asarray([t[0] for _, t, _ in entries], dtype=np.int32))
+            else:
+                for r, (_, toks, _) in zip(reqs, entries):
+                    r.prefix_len, r.fill_len = r.kv_len, r.kv_len + len(toks)
+                batch = ScheduleBatch(reqs=reqs, forward_mode=ForwardMode.EXTEND)
+                if not self._prepare_for_extend(batch):
+                    raise RuntimeError("replay: out of KV pages")
+            batch.logit_rows = np.asarray(rows, dtype=np.int64)
+            res = self.run_batch(batch)
+            res.wait()
+            self.forward_ct += 1
+            if res.row_logits is not None:
+                out = res.row_logits.float().cpu().numpy()
+        for rid in end:
+            r = live.pop(rid, None)
+            if r is not None:
+                self.kv.release(r, insert=False)
+        return out
+
     def _pick_retract_victims(self, rb: ScheduleBatch, force: bool) -> List[int]:
         """reference retract_decode:2825/2889 — retract the requests with the fewest generated tokens first
         (cheapest to recompute), longest prompts breaking ties"""

@@ -183,3 +183,24 @@ class HostKVPool:
 
     def free(self, pages) -> None:
         self._free.extend(int(p) for p in pages)
+
+
+class LayeredStatePool:
+    """Recurrent state of models whose recurrent layers differ in size: per layer ``conv[i]`` [slots, channels_i, taps_i - 1] (the last
+    inputs of the short convolution, model dtype) and ``ssm[i]`` [slots, heads_i, key_dim_i, value_dim_i] (fp32 matrix state), both indexed
+    by the request slot like the page table.  The two lists index like ``MambaPool``'s stacked tensors (``pool.conv[layer]``), so a mixer
+    written against one works against the other.  A slot needs no clearing on reuse: the kernels start a request whose cached length is
+    zero from a zero state and zero convolution history."""
+
+    def __init__(self, slots: int, geometry, dtype: torch.dtype, device):
+        """geometry: one ``(conv_channels, taps, heads, key_dim, value_dim)`` per recurrent layer"""
+        self.slots = slots
+        self.conv = [torch.zeros(slots, c, max(1, k - 1), dtype=dtype, device=device) for c, k, _, _, _ in geometry]
+        self.ssm = [torch.zeros(slots, h, dk, dv, dtype=torch.float32, device=device) for _, _, h, dk, dv in geometry]
+
+    def bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in self.conv + self.ssm)
+
+    def copy_row(self, src: int, dst: int) -> None:
+        for t in self.conv + self.ssm:
+            t[dst].copy_(t[src])

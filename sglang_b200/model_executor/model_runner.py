@@ -74,6 +74,7 @@ class BatchResult:
         self.d2h_bytes = 0
         self.accept_lens = None
         self.accepted_tokens = None
+        self.row_logits: Optional[torch.Tensor] = None     # fp32 [len(batch.logit_rows), vocab] when the batch asked for rows
 
     def wait(self) -> None:
         if self.next_token_ids is not None or self._tok_host is None:
@@ -292,8 +293,18 @@ class ModelRunner:
         pool = self.kv_pool.mamba
         ctx = torch.cuda.stream(self.stream) if self.is_cuda else _null_ctx()
         with ctx:
+            if hasattr(pool, "copy_row"):          # per-layer geometry (mem_cache/memory_pool.py LayeredStatePool)
+                pool.copy_row(src, dst)
+                return
             pool.conv[:, dst].copy_(pool.conv[:, src])
             pool.ssm[:, dst].copy_(pool.ssm[:, src])
+
+    def set_next_tokens(self, req_slots: np.ndarray, tokens: np.ndarray) -> None:
+        """force the next decode input of these request slots (where sampling would have left its choice), ordered on the runner's stream"""
+        ctx = torch.cuda.stream(self.stream) if self.is_cuda else _null_ctx()
+        with ctx:
+            idx = torch.from_numpy(np.ascontiguousarray(req_slots, dtype=np.int64)).to(self.device)
+            self.next_token_buf[idx] = torch.from_numpy(np.ascontiguousarray(tokens, dtype=np.int32)).to(self.device)
 
     def get_eos_token_ids(self) -> List[int]:
         return self.cfg.eos_token_ids
@@ -558,6 +569,9 @@ class ModelRunner:
             return self._pp_result(sb, res)
         samp_rows = np.arange(B) if decode else np.flatnonzero(sb.sample_mask)
         res.sample_rows = samp_rows
+        if sb.logit_rows is not None and len(sb.logit_rows):
+            rows = torch.from_numpy(np.ascontiguousarray(sb.logit_rows, dtype=np.int64)).to(self.device)
+            res.row_logits = self.model.compute_logits(hidden.index_select(0, rows)).float()
         if _dp is not None:
             # DP-attention: the LM head is vocab-parallel over ALL groups -> every group calls it exactly twice per forward (sampled
             # rows, then the rows of a prompt-logprob pass), with zero rows when it has nothing to contribute

@@ -142,6 +142,9 @@ def _register_builtins() -> None:
     register_model("Qwen3Model", type("Qwen3EmbeddingModel", (_emb.LlamaEmbeddingModel, _REGISTRY["Qwen3ForCausalLM"]), {}))
     register_model("MistralModel", _emb.LlamaEmbeddingModel)
     register_model("Qwen2Model", type("Qwen2EmbeddingModel", (_emb.LlamaEmbeddingModel,), {}))
+    from . import rirotar as _rr
+
+    register_model("Rirotar", _rr.RirotarForCausalLM)
     from . import transformers_fallback as _tff
 
     register_model("TransformersForCausalLM", _tff.TransformersForCausalLM)

@@ -434,3 +434,56 @@ def apply_penalties(logits, counts, prompt_mask, freq, pres, rep) -> None:
 
 def merge_attn_states(o1, lse1, o2, lse2):
     return torch_ref.merge_attn_states(o1, lse1, o2, lse2)
+
+
+# ------------------------------------------------------------------ fp32 residual stream / latent attention / gated delta rule / clamped GLU
+def add_rmsnorm_f32(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float, zero_centred: bool = False,
+                    out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """fp32 residual stream: ``residual += delta`` (in place, fp32 sum) and the RMS norm of the new residual in ``out_dtype``, one kernel
+    (csrc/kernels/residual_f32.cu).  ``zero_centred``: the weight is stored around zero and applied as ``1 + w``."""
+    if _use_native(residual) and residual.dtype == torch.float32 and residual.is_contiguous() and out_dtype in (torch.bfloat16, torch.float32) \
+            and (delta is None or (delta.dtype in (torch.bfloat16, torch.float32) and delta.is_contiguous())):
+        out = torch.empty(residual.shape, dtype=out_dtype, device=residual.device)
+        torch.ops.sglb.add_rmsnorm_f32(residual, delta, weight, out, float(eps), bool(zero_centred))
+        return out
+    return torch_ref.add_rmsnorm_f32(residual, delta, weight, eps, zero_centred, out_dtype)
+
+
+def clamped_glu(gu: torch.Tensor, limit: float, alpha: float = 1.702) -> torch.Tensor:
+    """[gate | up] halves -> min(g, limit) * sigmoid(alpha g) * (clamp(u, +-limit) + 1), fp32 math (csrc/kernels/residual_f32.cu)"""
+    if _use_native(gu) and gu.dtype in (torch.bfloat16, torch.float32) and gu.dim() == 2 and gu.is_contiguous():
+        out = torch.empty(gu.shape[0], gu.shape[1] // 2, dtype=gu.dtype, device=gu.device)
+        torch.ops.sglb.clamped_glu(gu, out, float(limit), float(alpha))
+        return out
+    return torch_ref.clamped_glu(gu, limit, alpha)
+
+
+def latent_attention(q_lat: torch.Tensor, cache: torch.Tensor, rank: int, page_table: torch.Tensor, req_slots: torch.Tensor, seq_lens: torch.Tensor,
+                     cu_q: Optional[torch.Tensor], q_lens: Optional[torch.Tensor], max_q_len: int, page_size: int, scale: float, window: int = -1,
+                     sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """absorbed multi-query attention over a paged cache of latent rows with a sliding window and per-head sinks
+    (csrc/kernels/latent_attention.cu; contract in ``torch_ref.latent_attention``).  ``cu_q`` None = one query per request."""
+    if _use_native(q_lat) and q_lat.dtype == torch.float32 and cache.dtype in (torch.bfloat16, torch.float32) and q_lat.is_contiguous():
+        out = torch.empty_like(q_lat)
+        torch.ops.sglb.latent_attention(q_lat, cache, int(rank), page_table, req_slots, seq_lens, cu_q, int(max_q_len), int(page_size),
+                                        float(scale), int(window), sinks, out)
+        return out
+    return torch_ref.latent_attention(q_lat, cache, rank, page_table, req_slots, seq_lens, q_lens, page_size, scale, window, sinks)
+
+
+def gated_delta_rule(u: torch.Tensor, Hk: int, Dk: int, H: int, Dv: int, a_raw: torch.Tensor, A_log: torch.Tensor, dt_bias: torch.Tensor,
+                     b_raw: torch.Tensor, state: torch.Tensor, req_slots: torch.Tensor, seq_lens: torch.Tensor, cu_q: Optional[torch.Tensor],
+                     q_lens: Optional[torch.Tensor], gate_raw: Optional[torch.Tensor] = None, norm_w: Optional[torch.Tensor] = None,
+                     eps: float = 1e-6, gate_act: str = "silu") -> torch.Tensor:
+    """gated delta rule over a ragged batch (prefill portions and single decode tokens alike): unit-norm q/k, decay and beta from their raw
+    projections, the fp32 state update and read-out, and the gated per-head RMS norm of the output, in one kernel
+    (csrc/kernels/delta_rule.cu; contract in ``torch_ref.gated_delta_rule``)."""
+    if _use_native(u) and u.dtype == torch.float32 and state.dtype == torch.float32 and Dk <= 256 and Dv <= 1024 and u.is_contiguous():
+        T = u.shape[0]
+        out = torch.empty(T, H, Dv, dtype=torch.float32, device=u.device)
+        f = lambda t: None if t is None else t.float().contiguous()
+        torch.ops.sglb.gated_delta_rule(u, int(Hk), int(Dk), int(H), int(Dv), f(a_raw), f(A_log), f(dt_bias), f(b_raw), state, req_slots, seq_lens,
+                                        cu_q, f(gate_raw), f(norm_w), float(eps), gate_act == "silu", out)
+        return out
+    return torch_ref.gated_delta_rule(u, Hk, Dk, H, Dv, a_raw, A_log, dt_bias, b_raw, state, req_slots, seq_lens, q_lens, gate_raw, norm_w, eps,
+                                      gate_act)

@@ -29,17 +29,18 @@ def topk_softmax(router_logits: torch.Tensor, top_k: int, renormalize: bool = Tr
 
 
 def fused_moe(x: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, topk_w: torch.Tensor, topk_ids: torch.Tensor,
-              expert_offset: int = 0) -> torch.Tensor:
+              expert_offset: int = 0, act=None) -> torch.Tensor:
+    """``act``: None = silu(gate) * up, else a callable on the [rows, 2I] gate|up block (e.g. the clamped GLU of ``ops.clamped_glu``)"""
     if not x.is_cuda:
-        return torch_ref.fused_moe(x, w13, w2, topk_w, topk_ids, expert_offset)
-    if _has("moe_grouped_mlp"):
+        return torch_ref.fused_moe(x, w13, w2, topk_w, topk_ids, expert_offset, act)
+    if act is None and x.dtype == torch.bfloat16 and _has("moe_grouped_mlp"):
         out = torch.empty_like(x)
         torch.ops.sglb.moe_grouped_mlp(x, w13, w2, topk_w, topk_ids, out, expert_offset)
         return out
-    return _fused_moe_sorted(x, w13, w2, topk_w, topk_ids, expert_offset)
+    return _fused_moe_sorted(x, w13, w2, topk_w, topk_ids, expert_offset, act)
 
 
-def _fused_moe_sorted(x, w13, w2, topk_w, topk_ids, expert_offset):
+def _fused_moe_sorted(x, w13, w2, topk_w, topk_ids, expert_offset, act=None):
     """sort (token, k) pairs by expert, run one GEMM pair per local expert on its contiguous slice, scatter-add."""
     T, H = x.shape
     E = w13.shape[0]
@@ -58,7 +59,7 @@ def _fused_moe_sorted(x, w13, w2, topk_w, topk_ids, expert_offset):
         if c == 0:
             continue
         h = linear(xs[off:off + c], w13[e])
-        h = silu_and_mul(h)
+        h = silu_and_mul(h) if act is None else act(h)
         y = linear(h, w2[e]).float() * ws[off:off + c, None]
         out.index_add_(0, tok[off:off + c], y)
         off += c

@@ -258,7 +258,7 @@ def moe_topk_softmax(router_logits: torch.Tensor, top_k: int, renormalize: bool 
 
 
 def fused_moe(x: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, topk_w: torch.Tensor, topk_ids: torch.Tensor,
-              expert_offset: int = 0) -> torch.Tensor:
+              expert_offset: int = 0, act=None) -> torch.Tensor:
     """x [T,H]; w13 [E_local, 2I, H]; w2 [E_local, H, I]; ids are global expert ids; experts outside
     [expert_offset, expert_offset+E_local) contribute zero (EP)."""
     T, H = x.shape
@@ -270,7 +270,7 @@ def fused_moe(x: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, topk_w: torc
         if tok.numel() == 0:
             continue
         h = F.linear(x[tok], w13[e])
-        h = silu_and_mul(h)
+        h = silu_and_mul(h) if act is None else act(h)
         y = F.linear(h, w2[e]).float()
         out.index_add_(0, tok, y * topk_w[tok, kk].float()[:, None])
     return out.to(x.dtype)
@@ -376,3 +376,102 @@ def selective_state_update(state: torch.Tensor, req_slots: torch.Tensor, x: torc
     if D is not None:
         y = y + D.float()[None, :, None] * xh
     return y
+
+
+# ------------------------------------------------------------------ fp32 residual stream, latent attention, gated delta rule, clamped GLU
+def add_rmsnorm_f32(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float, zero_centred: bool,
+                    out_dtype: torch.dtype) -> torch.Tensor:
+    """residual (fp32, in place) += delta; returns norm(residual) * (1 + w | w) in ``out_dtype``"""
+    if delta is not None:
+        residual.add_(delta.float())
+    y = residual * torch.rsqrt(residual.pow(2).mean(-1, keepdim=True) + eps)
+    w = weight.float()
+    return (y * (1.0 + w if zero_centred else w)).to(out_dtype)
+
+
+def clamped_glu(gu: torch.Tensor, limit: float, alpha: float = 1.702) -> torch.Tensor:
+    """gu [T, 2I] = [gate | up] -> min(g, limit) * sigmoid(alpha * g) * (clamp(u, -limit, limit) + 1)"""
+    I = gu.shape[-1] // 2
+    g = gu[..., :I].float().clamp(max=limit)
+    u = gu[..., I:].float().clamp(-limit, limit)
+    return (g * torch.sigmoid(alpha * g) * (u + 1.0)).to(gu.dtype)
+
+
+def latent_attention(q_lat: torch.Tensor, cache: torch.Tensor, rank: int, page_table: torch.Tensor, req_slots: torch.Tensor, seq_lens: torch.Tensor,
+                     q_lens: Optional[torch.Tensor], page_size: int, scale: float, window: int, sinks: Optional[torch.Tensor]) -> torch.Tensor:
+    """absorbed multi-query attention over cached latent rows.  q_lat fp32 [T, H, rank] (query already multiplied into the key up-projection);
+    cache [slots, 1, >= rank]; key j of a request is visible to its query i when ``0 <= i - j < window`` (``window <= 0``: all earlier keys);
+    ``sinks`` fp32 [H]: exp(sink_h) joins the soft-max denominator only.  Returns the probability-weighted latent rows, fp32 [T, H, rank]."""
+    T, H, R = q_lat.shape
+    out = torch.empty(T, H, R, dtype=torch.float32, device=q_lat.device)
+    qs = 0
+    for b in range(req_slots.shape[0]):
+        L = int(seq_lens[b])
+        ql = 1 if q_lens is None else int(q_lens[b])
+        if ql <= 0:
+            continue
+        lo = 0 if window <= 0 else max(0, L - ql - window + 1)
+        pos = torch.arange(lo, L, device=q_lat.device)
+        slots = page_table[int(req_slots[b]), (pos // page_size).long()].long() * page_size + pos % page_size
+        C = cache[slots, 0, :R].float()                                    # [n, R]
+        s = torch.einsum("qhr,kr->hqk", q_lat[qs:qs + ql].float(), C) * scale
+        qpos = torch.arange(L - ql, L, device=q_lat.device)[:, None]
+        hide = pos[None, :] > qpos
+        if window > 0:
+            hide = hide | (pos[None, :] <= qpos - window)
+        s = s.masked_fill(hide[None], float("-inf"))
+        if sinks is not None:
+            s = torch.cat([s, sinks.float()[:, None, None].expand(H, ql, 1)], -1)
+        p = torch.softmax(s, dim=-1)[..., : pos.numel()]
+        out[qs:qs + ql] = torch.einsum("hqk,kr->qhr", p, C)
+        qs += ql
+    return out
+
+
+def gated_delta_rule(u: torch.Tensor, Hk: int, Dk: int, H: int, Dv: int, a_raw: torch.Tensor, A_log: torch.Tensor, dt_bias: torch.Tensor,
+                     b_raw: torch.Tensor, state: torch.Tensor, req_slots: torch.Tensor, seq_lens: torch.Tensor, q_lens: Optional[torch.Tensor],
+                     gate_raw: Optional[torch.Tensor] = None, norm_w: Optional[torch.Tensor] = None, eps: float = 1e-6,
+                     gate_act: str = "silu") -> torch.Tensor:
+    """Gated delta rule over a ragged batch, token by token, state in place.
+
+    u fp32 [T, 2*Hk*Dk + H*Dv] = short-conv outputs [q | k | v] (not yet normalised); value head h reads q/k head ``h // (H // Hk)``.
+    a_raw [T, H] (one decay per head) or [T, H*Dk] (one per head and key channel): decay = exp(-exp(A_log_h) * softplus(a_raw + dt_bias)).
+    b_raw [T, H]: beta = sigmoid(b_raw).  state fp32 [slots, H, Dk, Dv]; a request whose ``seq_len == q_len`` starts from zero.
+    Per token: S <- decay * S (rows = key channels); w = beta * (v - S^T k); S <- S + k w^T; o = S^T q  (q, k unit vectors, q also / sqrt(Dk)).
+    With ``norm_w``: o <- o / rms(o) * norm_w * act(gate_raw) per head (act = silu | sigmoid).  Returns fp32 [T, H, Dv]."""
+    T = u.shape[0]
+    kd = Hk * Dk
+    rep = H // Hk
+    q = u[:, :kd].float().view(T, Hk, Dk)
+    k = u[:, kd:2 * kd].float().view(T, Hk, Dk)
+    v = u[:, 2 * kd:].float().view(T, H, Dv)
+    q = q * torch.rsqrt((q * q).sum(-1, keepdim=True) + 1e-6) * Dk ** -0.5
+    k = k * torch.rsqrt((k * k).sum(-1, keepdim=True) + 1e-6)
+    q, k = q.repeat_interleave(rep, 1), k.repeat_interleave(rep, 1)
+    per_channel = a_raw.shape[1] != H
+    sp = F.softplus(a_raw.float() + dt_bias.float())
+    if per_channel:
+        g = torch.exp(-A_log.float().exp()[None, :, None] * sp.view(T, H, Dk))
+    else:
+        g = torch.exp(-A_log.float().exp()[None, :] * sp)[..., None].expand(T, H, Dk)
+    beta = torch.sigmoid(b_raw.float())
+    out = torch.empty(T, H, Dv, dtype=torch.float32, device=u.device)
+    off = 0
+    for b in range(req_slots.shape[0]):
+        n = 1 if q_lens is None else int(q_lens[b])
+        if n <= 0:
+            continue
+        slot = int(req_slots[b])
+        S = torch.zeros_like(state[slot]) if int(seq_lens[b]) - n == 0 else state[slot].clone()
+        for t in range(off, off + n):
+            S = S * g[t][..., None]
+            w = beta[t][:, None] * (v[t] - torch.einsum("hkv,hk->hv", S, k[t]))
+            S = S + k[t][..., None] * w[:, None, :]
+            out[t] = torch.einsum("hkv,hk->hv", S, q[t])
+        state[slot] = S
+        off += n
+    if norm_w is not None:
+        out = out * torch.rsqrt(out.pow(2).mean(-1, keepdim=True) + eps) * norm_w.float()
+        z = gate_raw.float().view(T, H, Dv)
+        out = out * (F.silu(z) if gate_act == "silu" else torch.sigmoid(z))
+    return out
