@@ -220,6 +220,78 @@ void gated_delta_update(at::Tensor state, const at::Tensor& req_slots, const at:
   count();
 }
 
+void add_rmsnorm_f32(at::Tensor residual, c10::optional<at::Tensor> delta, const at::Tensor& w, at::Tensor out, double eps, bool zero_centred) {
+  CHECK_CUDA(residual);
+  TORCH_CHECK(residual.scalar_type() == at::kFloat && residual.dim() == 2 && residual.is_contiguous() && out.is_contiguous() && w.is_contiguous());
+  TORCH_CHECK(out.scalar_type() == w.scalar_type() && (out.scalar_type() == at::kFloat || out.scalar_type() == at::kBFloat16));
+  TORCH_CHECK(out.numel() == residual.numel() && w.numel() == residual.size(1));
+  bool dbf = false;
+  if (delta.has_value()) {
+    TORCH_CHECK(delta->is_contiguous() && delta->numel() == residual.numel() && (delta->scalar_type() == at::kFloat || delta->scalar_type() == at::kBFloat16));
+    dbf = delta->scalar_type() == at::kBFloat16;
+  }
+  c10::cuda::CUDAGuard g(residual.device());
+  sglb::add_rmsnorm_f32(residual.data_ptr<float>(), delta.has_value() ? delta->data_ptr() : nullptr, dbf, w.data_ptr(), out.data_ptr(),
+                        out.scalar_type() == at::kBFloat16, (int)residual.size(0), (int)residual.size(1), (float)eps, zero_centred, cur_stream());
+  count();
+}
+
+void clamped_glu(const at::Tensor& gu, at::Tensor out, double limit, double alpha) {
+  CHECK_CUDA(gu);
+  TORCH_CHECK(gu.dim() == 2 && gu.is_contiguous() && out.is_contiguous() && gu.scalar_type() == out.scalar_type() && gu.size(1) % 2 == 0 &&
+              out.numel() * 2 == gu.numel() && (gu.scalar_type() == at::kFloat || gu.scalar_type() == at::kBFloat16));
+  c10::cuda::CUDAGuard g(gu.device());
+  sglb::clamped_glu(gu.data_ptr(), out.data_ptr(), gu.scalar_type() == at::kBFloat16, (int)gu.size(0), (int)(gu.size(1) / 2), (float)limit,
+                    (float)alpha, cur_stream());
+  count();
+}
+
+void gated_delta_rule(const at::Tensor& u, int64_t Hk, int64_t Dk, int64_t H, int64_t Dv, const at::Tensor& a_raw, const at::Tensor& A_log,
+                      const at::Tensor& dt_bias, const at::Tensor& b_raw, at::Tensor state, const at::Tensor& req_slots, const at::Tensor& seq_lens,
+                      c10::optional<at::Tensor> cu_q, c10::optional<at::Tensor> gate_raw, c10::optional<at::Tensor> norm_w, double eps,
+                      bool gate_silu, bool per_channel, at::Tensor out) {
+  CHECK_CUDA(u); CHECK_I32(req_slots); CHECK_I32(seq_lens);
+  auto f32c = [](const at::Tensor& t) { return t.scalar_type() == at::kFloat && t.is_contiguous(); };
+  TORCH_CHECK(f32c(u) && f32c(a_raw) && f32c(A_log) && f32c(dt_bias) && f32c(b_raw) && f32c(state) && f32c(out) && u.dim() == 2);
+  const int64_t T = u.size(0);
+  const int B = (int)req_slots.size(0);
+  TORCH_CHECK(Hk > 0 && H % Hk == 0 && u.size(1) == 2 * Hk * Dk + H * Dv && state.dim() == 4 && state.size(1) == H && state.size(2) == Dk &&
+              state.size(3) == Dv && out.numel() == T * H * Dv && b_raw.numel() == T * H && A_log.numel() == H);
+  const int64_t nd = per_channel ? H * Dk : H;
+  TORCH_CHECK(a_raw.numel() == T * nd && dt_bias.numel() == nd, "gated_delta_rule: decay input must be [T, H] or (per channel) [T, H * Dk]");
+  TORCH_CHECK(gate_raw.has_value() == norm_w.has_value());
+  if (gate_raw.has_value()) TORCH_CHECK(f32c(*gate_raw) && f32c(*norm_w) && gate_raw->numel() == T * H * Dv && norm_w->numel() == Dv);
+  if (cu_q.has_value()) { CHECK_I32(*cu_q); TORCH_CHECK(cu_q->numel() == B + 1); } else TORCH_CHECK(T == B);
+  if (T == 0) return;
+  c10::cuda::CUDAGuard g(u.device());
+  const bool ok = sglb::gated_delta_rule(u.data_ptr<float>(), (int)u.stride(0), (int)Hk, (int)Dk, (int)H, (int)Dv, a_raw.data_ptr<float>(), per_channel,
+                                         A_log.data_ptr<float>(), dt_bias.data_ptr<float>(), b_raw.data_ptr<float>(), opt_ptr<float>(gate_raw),
+                                         opt_ptr<float>(norm_w), (float)eps, gate_silu, state.data_ptr<float>(), req_slots.data_ptr<int>(),
+                                         seq_lens.data_ptr<int>(), opt_ptr<int>(cu_q), B, out.data_ptr<float>(), cur_stream());
+  TORCH_CHECK(ok, "gated_delta_rule: head shape (key dim ", Dk, ", value dim ", Dv, ") does not fit one CTA per head");
+  count();
+}
+
+void latent_attention(const at::Tensor& q, const at::Tensor& cache, int64_t rank, const at::Tensor& page_table, const at::Tensor& req_slots,
+                      const at::Tensor& seq_lens, c10::optional<at::Tensor> cu_q, int64_t max_q_len, int64_t page_size, double scale, int64_t window,
+                      c10::optional<at::Tensor> sinks, at::Tensor out) {
+  CHECK_CUDA(q); CHECK_I32(page_table); CHECK_I32(req_slots); CHECK_I32(seq_lens);
+  TORCH_CHECK(q.scalar_type() == at::kFloat && q.dim() == 3 && q.is_contiguous() && out.scalar_type() == at::kFloat && out.is_contiguous() &&
+              out.numel() == q.numel() && q.size(2) == rank);
+  TORCH_CHECK((cache.scalar_type() == at::kFloat || cache.scalar_type() == at::kBFloat16) && cache.dim() == 3 && cache.size(1) == 1 &&
+              cache.stride(2) == 1 && cache.size(2) >= rank && page_table.dim() == 2 && page_table.stride(1) == 1);
+  const int B = (int)req_slots.size(0);
+  if (cu_q.has_value()) { CHECK_I32(*cu_q); TORCH_CHECK(cu_q->numel() == B + 1); } else TORCH_CHECK(q.size(0) == B);
+  if (sinks.has_value()) TORCH_CHECK(sinks->scalar_type() == at::kFloat && sinks->is_contiguous() && sinks->numel() == q.size(1));
+  if (q.size(0) == 0) return;
+  c10::cuda::CUDAGuard g(q.device());
+  sglb::latent_attention(q.data_ptr<float>(), cache.data_ptr(), cache.scalar_type() == at::kBFloat16, (int)cache.stride(0), (int)rank,
+                         page_table.data_ptr<int>(), (int)page_table.stride(0), (int)page_size, req_slots.data_ptr<int>(), seq_lens.data_ptr<int>(),
+                         opt_ptr<int>(cu_q), B, (int)max_q_len, (int)q.size(1), (float)scale, (int)window, opt_ptr<float>(sinks),
+                         out.data_ptr<float>(), cur_stream());
+  count();
+}
+
 // bench tool: per-role cycle accounting of the decode attention kernel into buf [ctas * 30] (int64); an empty tensor turns it off
 void attn_decode_prof(const at::Tensor& buf) {
   if (buf.numel() == 0) { sglb::attn_decode_set_prof(nullptr); return; }
@@ -613,6 +685,13 @@ TORCH_LIBRARY(sglb, m) {
     auto r = sglb::green_ctx_streams((int)device, c);
     return std::vector<int64_t>(r.begin(), r.end());
   });
+  m.def("add_rmsnorm_f32(Tensor(a!) residual, Tensor? delta, Tensor w, Tensor(b!) out, float eps, bool zero_centred) -> ()", &add_rmsnorm_f32);
+  m.def("clamped_glu(Tensor gu, Tensor(a!) out, float limit, float alpha) -> ()", &clamped_glu);
+  m.def("gated_delta_rule(Tensor u, int Hk, int Dk, int H, int Dv, Tensor a_raw, Tensor A_log, Tensor dt_bias, Tensor b_raw, Tensor(a!) state, "
+        "Tensor req_slots, Tensor seq_lens, Tensor? cu_q, Tensor? gate_raw, Tensor? norm_w, float eps, bool gate_silu, bool per_channel, Tensor(b!) out) -> ()",
+        &gated_delta_rule);
+  m.def("latent_attention(Tensor q, Tensor cache, int rank, Tensor page_table, Tensor req_slots, Tensor seq_lens, Tensor? cu_q, int max_q_len, "
+        "int page_size, float scale, int window, Tensor? sinks, Tensor(a!) out) -> ()", &latent_attention);
   m.def("gated_delta_update(Tensor(a!) state, Tensor req_slots, Tensor u, Tensor g, Tensor beta, int Hk, Tensor(b!) out) -> ()", &gated_delta_update);
   m.def("causal_conv1d(Tensor x, Tensor w, Tensor? bias, Tensor(a!) conv_state, Tensor? cu_q, Tensor req_slots, Tensor seq_lens, int max_q_len, "
         "bool silu, Tensor(b!) u) -> ()", &causal_conv1d);

@@ -100,6 +100,18 @@ void selective_state_update(float* state, const int* req_slots, const float* x, 
                             const float* Cm, int ldbc, const float* Dv, int B, int H, int P, int N, int G, float* y, cudaStream_t stream);
 bool gated_delta_update(float* state, const int* req_slots, const float* u, int ldu, int k_off, int v_off, const float* g, const float* beta, int B,
                         int Hv, int r, int Dk, int Dv, float* out, cudaStream_t stream);
+// residual_f32.cu
+void add_rmsnorm_f32(float* residual, const void* delta, bool delta_bf16, const void* w, void* out, bool out_bf16, int T, int H, float eps,
+                     bool zero_centred, cudaStream_t stream);
+void clamped_glu(const void* gu, void* out, bool bf16, int T, int I, float limit, float alpha, cudaStream_t stream);
+// delta_rule.cu
+bool gated_delta_rule(const float* u, int ldu, int Hk, int Dk, int H, int Dv, const float* a_raw, bool per_channel, const float* A_log,
+                      const float* dt_bias, const float* b_raw, const float* gate_raw, const float* norm_w, float eps, bool gate_silu, float* state,
+                      const int* req_slots, const int* seq_lens, const int* cu_q, int B, float* out, cudaStream_t stream);
+// latent_attention.cu
+void latent_attention(const float* q, const void* cache, bool cache_bf16, int ldc, int R, const int* page_table, int pt_stride, int page_size,
+                      const int* req_slots, const int* seq_lens, const int* cu_q, int B, int max_q_len, int H, float scale, int window,
+                      const float* sinks, float* out, cudaStream_t stream);
 void greedy_shard(const void* logits, bool bf16, int B, int stride, int v_valid, int v_offset, int rank, int tp, int b_pad, void* buf,
                   cudaStream_t stream);
 void greedy_merge(const void* buf, int tp, int b_pad, int B, const int* out_slots, int* next_token_buf, int* out_tokens, cudaStream_t stream);

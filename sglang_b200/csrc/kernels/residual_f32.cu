@@ -1,0 +1,98 @@
+// fp32 residual stream helpers.
+//
+//   add_rmsnorm_f32 : residual (fp32, in place) += delta (bf16 | fp32 | none); out = residual / rms(residual) * (w | 1 + w) in bf16 | fp32.
+//                     One block per row; the sum, the mean of squares and the scaling are fp32, eps sits inside the root.
+//   clamped_glu     : [gate | up] halves -> min(g, limit) * sigmoid(alpha * g) * (clamp(u, -limit, limit) + 1), fp32 math.
+#include <stdexcept>
+
+#include "common.cuh"
+#include "tma_host.h"
+
+namespace sglb {
+namespace {
+
+template <typename T> __device__ __forceinline__ float ldf(const T* p);
+template <> __device__ __forceinline__ float ldf<float>(const float* p) { return *p; }
+template <> __device__ __forceinline__ float ldf<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+template <typename T> __device__ __forceinline__ void stf(T* p, float v);
+template <> __device__ __forceinline__ void stf<float>(float* p, float v) { *p = v; }
+template <> __device__ __forceinline__ void stf<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16(v); }
+
+template <typename TD, typename TO>
+__global__ void __launch_bounds__(256) add_rmsnorm_f32_kernel(float* __restrict__ res, const TD* __restrict__ delta, const TO* __restrict__ w,
+                                                              TO* __restrict__ out, int H, float eps, int zero_centred) {
+  __shared__ float red[8];
+  __shared__ float s_rs;
+  float* r = res + (size_t)blockIdx.x * H;
+  const TD* d = delta ? delta + (size_t)blockIdx.x * H : nullptr;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < H; i += 256) {
+    float v = r[i];
+    if (d) {
+      v += ldf<TD>(d + i);
+      r[i] = v;
+    }
+    ss += v * v;
+  }
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float t = threadIdx.x < 8 ? red[threadIdx.x] : 0.f;
+    t = warp_sum(t);
+    if (threadIdx.x == 0) s_rs = 1.0f / sqrtf(t / (float)H + eps);
+  }
+  __syncthreads();
+  const float rs = s_rs;
+  TO* o = out + (size_t)blockIdx.x * H;
+  for (int i = threadIdx.x; i < H; i += 256) {          // each thread re-reads exactly the elements it wrote
+    float wv = ldf<TO>(w + i);
+    if (zero_centred) wv += 1.f;
+    stf<TO>(o + i, r[i] * rs * wv);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) clamped_glu_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, float limit, float alpha) {
+  const T* row = gu + (size_t)blockIdx.x * 2 * I;
+  const int i = blockIdx.y * 256 + threadIdx.x;
+  if (i >= I) return;
+  const float g = fminf(ldf<T>(row + i), limit);
+  const float u = fminf(fmaxf(ldf<T>(row + I + i), -limit), limit);
+  stf<T>(out + (size_t)blockIdx.x * I + i, g / (1.f + expf(-alpha * g)) * (u + 1.f));
+}
+
+}  // namespace
+
+void add_rmsnorm_f32(float* residual, const void* delta, bool delta_bf16, const void* w, void* out, bool out_bf16, int T, int H, float eps,
+                     bool zero_centred, cudaStream_t stream) {
+  if (T <= 0) return;
+  const int z = zero_centred ? 1 : 0;
+  if (out_bf16) {
+    if (delta_bf16)
+      add_rmsnorm_f32_kernel<__nv_bfloat16, __nv_bfloat16><<<T, 256, 0, stream>>>(residual, (const __nv_bfloat16*)delta, (const __nv_bfloat16*)w,
+                                                                                  (__nv_bfloat16*)out, H, eps, z);
+    else
+      add_rmsnorm_f32_kernel<float, __nv_bfloat16><<<T, 256, 0, stream>>>(residual, (const float*)delta, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, H,
+                                                                          eps, z);
+  } else {
+    if (delta_bf16)
+      add_rmsnorm_f32_kernel<__nv_bfloat16, float><<<T, 256, 0, stream>>>(residual, (const __nv_bfloat16*)delta, (const float*)w, (float*)out, H, eps, z);
+    else
+      add_rmsnorm_f32_kernel<float, float><<<T, 256, 0, stream>>>(residual, (const float*)delta, (const float*)w, (float*)out, H, eps, z);
+  }
+  SGLB_CUDA_CHECK(cudaGetLastError());
+}
+
+void clamped_glu(const void* gu, void* out, bool bf16, int T, int I, float limit, float alpha, cudaStream_t stream) {
+  if (T <= 0 || I <= 0) return;
+  if ((I + 255) / 256 > 65535) throw std::runtime_error("sglb clamped_glu: feed-forward width too large for one launch");
+  dim3 g(T, (I + 255) / 256);
+  if (bf16)
+    clamped_glu_kernel<__nv_bfloat16><<<g, 256, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, I, limit, alpha);
+  else
+    clamped_glu_kernel<float><<<g, 256, 0, stream>>>((const float*)gu, (float*)out, I, limit, alpha);
+  SGLB_CUDA_CHECK(cudaGetLastError());
+}
+
+}  // namespace sglb

@@ -53,7 +53,7 @@ def main(argv=None) -> int:
     pages = (ns.max_tokens + PAGE - 1) // PAGE
     args = ServerArgs(model_path=ns.model, device=device, skip_tokenizer_init=True, page_size=PAGE, max_total_tokens=pages * PAGE,
                       max_running_requests=SLOTS, context_length=pages * PAGE, disable_radix_cache=True, disable_cuda_graph=True,
-                      disable_overlap_schedule=True, chunked_prefill_size=-1, max_prefill_tokens=1 << 30, log_level="warning",
+                      disable_overlap_schedule=True, chunked_prefill_size=-1, max_prefill_tokens=pages * PAGE, log_level="warning",
                       json_model_override_args=json.dumps({"dtype": ns.dtype}))
     eng = Engine(server_args=args)
     os.makedirs(ns.out, exist_ok=True)

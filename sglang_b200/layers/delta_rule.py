@@ -115,5 +115,5 @@ class GatedDeltaMixer(nn.Module):
             gate_raw = ops.linear(gate_raw.contiguous(), self.g_up)
             a_raw = ops.linear(a_raw.contiguous(), self.a_up)
         o = ops.gated_delta_rule(u, self.Hk, self.Dk, H, self.Dv, a_raw, self.A_log, self.dt_bias, b_raw, pool.ssm[self.state_idx], fb.req_slots,
-                                 fb.seq_lens, fb.cu_q, fb.q_lens, gate_raw, self.norm_weight, self.eps, self.gate_act)
+                                 fb.seq_lens, fb.cu_q, fb.q_lens, gate_raw, self.norm_weight, self.eps, self.gate_act, self.decay == "channel")
         return ops.linear(o.view(T, vd).to(h.dtype), self.o_weight)

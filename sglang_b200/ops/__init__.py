@@ -474,16 +474,18 @@ def latent_attention(q_lat: torch.Tensor, cache: torch.Tensor, rank: int, page_t
 def gated_delta_rule(u: torch.Tensor, Hk: int, Dk: int, H: int, Dv: int, a_raw: torch.Tensor, A_log: torch.Tensor, dt_bias: torch.Tensor,
                      b_raw: torch.Tensor, state: torch.Tensor, req_slots: torch.Tensor, seq_lens: torch.Tensor, cu_q: Optional[torch.Tensor],
                      q_lens: Optional[torch.Tensor], gate_raw: Optional[torch.Tensor] = None, norm_w: Optional[torch.Tensor] = None,
-                     eps: float = 1e-6, gate_act: str = "silu") -> torch.Tensor:
+                     eps: float = 1e-6, gate_act: str = "silu", per_channel: Optional[bool] = None) -> torch.Tensor:
     """gated delta rule over a ragged batch (prefill portions and single decode tokens alike): unit-norm q/k, decay and beta from their raw
     projections, the fp32 state update and read-out, and the gated per-head RMS norm of the output, in one kernel
     (csrc/kernels/delta_rule.cu; contract in ``torch_ref.gated_delta_rule``)."""
-    if _use_native(u) and u.dtype == torch.float32 and state.dtype == torch.float32 and Dk <= 256 and Dv <= 1024 and u.is_contiguous():
+    if per_channel is None:
+        per_channel = a_raw.shape[1] != H
+    if _use_native(u) and u.dtype == torch.float32 and state.dtype == torch.float32 and u.is_contiguous():
         T = u.shape[0]
         out = torch.empty(T, H, Dv, dtype=torch.float32, device=u.device)
         f = lambda t: None if t is None else t.float().contiguous()
         torch.ops.sglb.gated_delta_rule(u, int(Hk), int(Dk), int(H), int(Dv), f(a_raw), f(A_log), f(dt_bias), f(b_raw), state, req_slots, seq_lens,
-                                        cu_q, f(gate_raw), f(norm_w), float(eps), gate_act == "silu", out)
+                                        cu_q, f(gate_raw), f(norm_w), float(eps), gate_act == "silu", bool(per_channel), out)
         return out
     return torch_ref.gated_delta_rule(u, Hk, Dk, H, Dv, a_raw, A_log, dt_bias, b_raw, state, req_slots, seq_lens, q_lens, gate_raw, norm_w, eps,
-                                      gate_act)
+                                      gate_act, per_channel)

@@ -431,7 +431,7 @@ def latent_attention(q_lat: torch.Tensor, cache: torch.Tensor, rank: int, page_t
 def gated_delta_rule(u: torch.Tensor, Hk: int, Dk: int, H: int, Dv: int, a_raw: torch.Tensor, A_log: torch.Tensor, dt_bias: torch.Tensor,
                      b_raw: torch.Tensor, state: torch.Tensor, req_slots: torch.Tensor, seq_lens: torch.Tensor, q_lens: Optional[torch.Tensor],
                      gate_raw: Optional[torch.Tensor] = None, norm_w: Optional[torch.Tensor] = None, eps: float = 1e-6,
-                     gate_act: str = "silu") -> torch.Tensor:
+                     gate_act: str = "silu", per_channel: Optional[bool] = None) -> torch.Tensor:
     """Gated delta rule over a ragged batch, token by token, state in place.
 
     u fp32 [T, 2*Hk*Dk + H*Dv] = short-conv outputs [q | k | v] (not yet normalised); value head h reads q/k head ``h // (H // Hk)``.
@@ -448,7 +448,8 @@ def gated_delta_rule(u: torch.Tensor, Hk: int, Dk: int, H: int, Dv: int, a_raw: 
     q = q * torch.rsqrt((q * q).sum(-1, keepdim=True) + 1e-6) * Dk ** -0.5
     k = k * torch.rsqrt((k * k).sum(-1, keepdim=True) + 1e-6)
     q, k = q.repeat_interleave(rep, 1), k.repeat_interleave(rep, 1)
-    per_channel = a_raw.shape[1] != H
+    if per_channel is None:
+        per_channel = a_raw.shape[1] != H
     sp = F.softplus(a_raw.float() + dt_bias.float())
     if per_channel:
         g = torch.exp(-A_log.float().exp()[None, :, None] * sp.view(T, H, Dk))

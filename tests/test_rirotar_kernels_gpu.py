@@ -1,0 +1,119 @@
+"""CUDA kernels of the Rirotar mechanisms against plain fp32 PyTorch references of the same ops (``ops.torch_ref``), which the CPU tests in
+``test_rirotar.py`` check against the token-by-token oracle."""
+import pytest
+import torch
+
+from sglang_b200 import ops
+from sglang_b200.ops import torch_ref
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _native():
+    assert ops.load_native(), "CUDA extension not built"
+
+
+@pytest.mark.parametrize("H", [96, 256, 1000])
+@pytest.mark.parametrize("ddt,odt", [(torch.bfloat16, torch.bfloat16), (torch.float32, torch.float32), (None, torch.bfloat16)])
+def test_add_rmsnorm_f32(H, ddt, odt):
+    _native()
+    g = torch.Generator(device=DEV).manual_seed(H)
+    res = torch.randn(7, H, device=DEV, generator=g) * 3
+    delta = None if ddt is None else torch.randn(7, H, device=DEV, generator=g).to(ddt)
+    w = (torch.randn(H, device=DEV, generator=g) * 0.2).to(odt)
+    for zc in (True, False):
+        r1, r2 = res.clone(), res.clone()
+        o1 = ops.add_rmsnorm_f32(r1, delta, w, 1e-5, zc, odt)
+        o2 = torch_ref.add_rmsnorm_f32(r2, delta, w, 1e-5, zc, odt)
+        assert o1.dtype == odt
+        torch.testing.assert_close(r1, r2, rtol=0, atol=0)
+        torch.testing.assert_close(o1.float(), o2.float(), rtol=1e-2 if odt == torch.bfloat16 else 2e-6, atol=1e-2 if odt == torch.bfloat16 else 2e-6)
+
+
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float32])
+def test_clamped_glu(dt):
+    _native()
+    gu = (torch.randn(33, 2 * 70, device=DEV) * 3).to(dt)
+    a = ops.clamped_glu(gu, 1.5)
+    b = torch_ref.clamped_glu(gu, 1.5)
+    torch.testing.assert_close(a.float(), b.float(), rtol=1e-2 if dt == torch.bfloat16 else 1e-6, atol=1e-2 if dt == torch.bfloat16 else 1e-6)
+
+
+def _paged(seq_lens, page_size, width, dtype, seed):
+    """a page table whose pages are scattered over the pool, and a cache full of values"""
+    g = torch.Generator().manual_seed(seed)
+    need = [(-(-L // page_size)) for L in seq_lens]
+    total = sum(need) + 3
+    perm = (torch.randperm(total - 1, generator=g) + 1).tolist()
+    pt = torch.zeros(len(seq_lens) + 2, max(need) + 1, dtype=torch.int32)
+    slots = [2, 0, 3, 1][: len(seq_lens)]
+    for b, n in enumerate(need):
+        for c in range(n):
+            pt[slots[b], c] = perm.pop()
+    cache = torch.randn(total * page_size, 1, width, generator=g).to(dtype)
+    return pt.to(DEV), torch.tensor(slots, dtype=torch.int32, device=DEV), cache.to(DEV)
+
+
+@pytest.mark.parametrize("cdt", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("R,H,window", [(40, 5, 19), (64, 6, 136), (128, 3, -1), (24, 17, 1)])
+def test_latent_attention_prefill_and_decode(cdt, R, H, window):
+    _native()
+    ps = 16
+    seq = [75, 203, 9, 130]
+    ql = [75, 37, 2, 1]
+    pt, slots, cache = _paged(seq, ps, R + 8, cdt, R)
+    g = torch.Generator(device=DEV).manual_seed(1)
+    sinks = torch.randn(H, device=DEV, generator=g)
+    sl = torch.tensor(seq, dtype=torch.int32, device=DEV)
+    q_lens = torch.tensor(ql, dtype=torch.int32, device=DEV)
+    cu = torch.zeros(5, dtype=torch.int32, device=DEV)
+    cu[1:] = torch.cumsum(q_lens, 0)
+    q = torch.randn(sum(ql), H, R, device=DEV, generator=g) * 0.5
+    for sk in (sinks, None):
+        a = ops.latent_attention(q, cache, R, pt, slots, sl, cu, q_lens, max(ql), ps, 0.3, window, sk)
+        b = torch_ref.latent_attention(q, cache, R, pt, slots, sl, q_lens, ps, 0.3, window, sk)
+        torch.testing.assert_close(a, b, rtol=2e-5, atol=2e-5)
+    # decode: one query per request
+    qd = torch.randn(4, H, R, device=DEV, generator=g) * 0.5
+    a = ops.latent_attention(qd, cache, R, pt, slots, sl, None, None, 1, ps, 0.3, window, sinks)
+    b = torch_ref.latent_attention(qd, cache, R, pt, slots, sl, None, ps, 0.3, window, sinks)
+    torch.testing.assert_close(a, b, rtol=2e-5, atol=2e-5)
+
+
+@pytest.mark.parametrize("Hk,H,Dk,Dv,chan", [(1, 2, 32, 32, False), (4, 4, 32, 32, True), (2, 6, 24, 40, True), (2, 4, 128, 128, False),
+                                             (1, 2, 64, 256, True), (1, 1, 200, 64, False), (3, 3, 8, 16, True)])
+def test_gated_delta_rule(Hk, H, Dk, Dv, chan):
+    _native()
+    g = torch.Generator(device=DEV).manual_seed(Dk * 7 + Dv)
+    ql = [19, 1, 30, 3]
+    seq = [19, 50, 44, 3]            # requests 0 and 3 are fresh, 1 is a decode step, 2 continues a prompt
+    T = sum(ql)
+    u = torch.randn(T, 2 * Hk * Dk + H * Dv, device=DEV, generator=g)
+    a_raw = torch.randn(T, H * Dk if chan else H, device=DEV, generator=g)
+    A_log = torch.randn(H, device=DEV, generator=g) * 0.5 - 1
+    dtb = torch.randn(H * Dk if chan else H, device=DEV, generator=g) * 0.5
+    b_raw = torch.randn(T, H, device=DEV, generator=g)
+    gate = torch.randn(T, H * Dv, device=DEV, generator=g)
+    nw = torch.randn(Dv, device=DEV, generator=g) * 0.2 + 1
+    state = torch.randn(6, H, Dk, Dv, device=DEV, generator=g) * 0.3
+    slots = torch.tensor([4, 1, 0, 5], dtype=torch.int32, device=DEV)
+    sl = torch.tensor(seq, dtype=torch.int32, device=DEV)
+    q_lens = torch.tensor(ql, dtype=torch.int32, device=DEV)
+    cu = torch.zeros(5, dtype=torch.int32, device=DEV)
+    cu[1:] = torch.cumsum(q_lens, 0)
+    for act in ("silu", "sigmoid"):
+        s1, s2 = state.clone(), state.clone()
+        o1 = ops.gated_delta_rule(u, Hk, Dk, H, Dv, a_raw, A_log, dtb, b_raw, s1, slots, sl, cu, q_lens, gate, nw, 1e-5, act, chan)
+        o2 = torch_ref.gated_delta_rule(u, Hk, Dk, H, Dv, a_raw, A_log, dtb, b_raw, s2, slots, sl, q_lens, gate, nw, 1e-5, act, chan)
+        torch.testing.assert_close(o1, o2, rtol=1e-4, atol=1e-5)
+        torch.testing.assert_close(s1, s2, rtol=1e-4, atol=1e-5)
+    # decode form (no cu_q) and raw read-out (no norm)
+    ud = u[:4].contiguous()
+    s1, s2 = state.clone(), state.clone()
+    sld = torch.tensor([7, 2, 9, 31], dtype=torch.int32, device=DEV)
+    o1 = ops.gated_delta_rule(ud, Hk, Dk, H, Dv, a_raw[:4].contiguous(), A_log, dtb, b_raw[:4].contiguous(), s1, slots, sld, None, None,
+                              per_channel=chan)
+    o2 = torch_ref.gated_delta_rule(ud, Hk, Dk, H, Dv, a_raw[:4], A_log, dtb, b_raw[:4], s2, slots, sld, None, per_channel=chan)
+    torch.testing.assert_close(o1, o2, rtol=1e-4, atol=1e-5)
+    torch.testing.assert_close(s1, s2, rtol=1e-4, atol=1e-5)
