@@ -61,7 +61,7 @@ def reset_launch_count() -> None:
 
 # ------------------------------------------------------------------ norms / activations
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: Optional[torch.Tensor] = None, gemma: bool = False) -> torch.Tensor:
-    if _use_native(x) and x.dtype == torch.bfloat16:
+    if _use_native(x) and x.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0 and x.shape[-1] <= 16384:      # (16-byte vector lanes)
         shp = x.shape
         x2 = x.reshape(-1, shp[-1])
         out = torch.empty_like(x2) if out is None else out.view(-1, shp[-1])
@@ -290,7 +290,7 @@ def apply_pt_delta(page_table: torch.Tensor, rows: torch.Tensor, cols: torch.Ten
 
 def embedding(weight: torch.Tensor, ids: torch.Tensor, gather_idx: Optional[torch.Tensor] = None, vocab_start: int = 0) -> torch.Tensor:
     T = ids.shape[0] if gather_idx is None else gather_idx.shape[0]
-    if _use_native(weight) and weight.dtype == torch.bfloat16:
+    if _use_native(weight) and weight.dtype == torch.bfloat16 and weight.shape[1] % 8 == 0:      # (16-byte vector lanes)
         out = torch.empty(T, weight.shape[1], dtype=weight.dtype, device=weight.device)
         torch.ops.sglb.embedding(weight, ids, gather_idx, out, vocab_start)
         return out
@@ -303,7 +303,7 @@ def embedding(weight: torch.Tensor, ids: torch.Tensor, gather_idx: Optional[torc
 
 
 def gather_rows(x: torch.Tensor, idx: torch.Tensor) -> torch.Tensor:
-    if _use_native(x) and x.dtype == torch.bfloat16:
+    if _use_native(x) and x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0:      # (16-byte vector lanes)
         out = torch.empty(idx.shape[0], x.shape[1], dtype=x.dtype, device=x.device)
         torch.ops.sglb.gather_rows(x, idx, out)
         return out

@@ -117,3 +117,74 @@ def test_gated_delta_rule(Hk, H, Dk, Dv, chan):
     o2 = torch_ref.gated_delta_rule(ud, Hk, Dk, H, Dv, a_raw[:4], A_log, dtb, b_raw[:4], s2, slots, sld, None, per_channel=chan)
     torch.testing.assert_close(o1, o2, rtol=1e-4, atol=1e-5)
     torch.testing.assert_close(s1, s2, rtol=1e-4, atol=1e-5)
+
+
+def test_latent_attention_standout_key_at_the_window_edge():
+    """a key whose latent row dominates the scores is seen by the last query inside the window and not by the next one (decode and portion)"""
+    _native()
+    R, H, W, ps = 48, 3, 33, 16
+    g = torch.Generator().manual_seed(4)
+    pages = torch.randperm(40, generator=g)[:12] + 1
+    pt = torch.zeros(3, 16, dtype=torch.int32)
+    pt[2, :12] = pages.int()
+    cache = torch.randn(48 * ps, 1, R, generator=g) * 0.1
+    mark = 63                                                   # last slot of a page
+    cache[int(pages[mark // ps]) * ps + mark % ps, 0, 0] = 5.0
+    cache, pt = cache.to(DEV), pt.to(DEV)
+    slots = torch.tensor([2], dtype=torch.int32, device=DEV)
+    for qpos in (mark + W - 1, mark + W):
+        q = torch.zeros(5, H, R, device=DEV)
+        q[-1, :, 0] = 6.0
+        sl = torch.tensor([qpos + 1], dtype=torch.int32, device=DEV)
+        dec = ops.latent_attention(q[-1:].contiguous(), cache, R, pt, slots, sl, None, None, 1, ps, 1.0, W, None)
+        ql = torch.tensor([5], dtype=torch.int32, device=DEV)
+        cu = torch.tensor([0, 5], dtype=torch.int32, device=DEV)
+        por = ops.latent_attention(q, cache, R, pt, slots, sl, cu, ql, 5, ps, 1.0, W, None)
+        ref = torch_ref.latent_attention(q, cache, R, pt, slots, sl, ql, ps, 1.0, W, None)
+        torch.testing.assert_close(por, ref, rtol=2e-5, atol=2e-5)
+        torch.testing.assert_close(dec, ref[-1:], rtol=2e-5, atol=2e-5)
+        assert (dec[0, 0, 0].item() > 4.0) == (qpos == mark + W - 1)
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", 3e-4), ("bfloat16", 0.08)])
+def test_engine_on_cuda_against_the_oracle(tmp_path, dtype, tol):
+    """the serving engine on the GPU (own kernels) against the token-by-token oracle: whole prompt, portions, decode, a mixed batch"""
+    import numpy as np
+
+    from test_rirotar import L, Harness, _attn, _cfg, _delta, _dense, _moe, _tokens
+
+    cfg = _cfg([L(_delta("delta", heads=4, kv_heads=2, dim=16, vdim=24), _dense(ff=64)), L(_attn(heads=4, dim=16, vdim=24, kv_rank=40, window=21), _moe(ff=32)),
+                L(_delta("channel_delta", heads=2, kv_heads=2, dim=40, vdim=16, conv=4, rank=8), _moe(experts=4, top=1, count=2, keep=2)),
+                L(_attn(heads=2, dim=8, vdim=8, kv_rank=24, window=70, scale=0.5), None)], width=64, vocab=96)
+    h = Harness(tmp_path, cfg, seed=9, device="cuda", dtype=dtype, page=16, max_tokens=1024)
+    a, b = _tokens(150, 96, 1), _tokens(77, 96, 2)
+    ra, rb = h.oracle(a), h.oracle(b)
+    if dtype == "float32":
+        err = lambda x, y: float(np.abs(x - y).max())
+    else:      # bf16 rounding can flip a close expert choice at single positions: judge the bulk (90th percentile of the per-position RMS error)
+        err = lambda x, y: float(np.quantile(np.sqrt(((x - y) ** 2).mean(-1)), 0.9))
+    assert err(h.step([("w", a, range(len(a)))], ["w"]), ra) < tol
+    assert err(h.run_cut("c", a, [2, 31, 16, 3, 64]), ra) < tol
+    # two requests interleaved: a portion of one beside single tokens of the other
+    o1 = h.step([("x", a[:100], range(100)), ("y", b[:5], range(5))])
+    got_a, got_b = [o1[:100]], [o1[100:]]
+    for i in range(50):
+        e = [("x", a[100 + i:101 + i], [0])]
+        if 5 + i < len(b):
+            e.append(("y", b[5 + i:6 + i], [0]))
+        o = h.step(e)
+        got_a.append(o[:1])
+        if len(e) > 1:
+            got_b.append(o[1:])
+    o = h.step([("y", b[55:], range(len(b) - 55))], ["x", "y"])
+    got_b.append(o)
+    assert err(np.concatenate(got_a), ra) < tol
+    assert err(np.concatenate(got_b), rb) < tol
+    outs = h.eng.generate(input_ids=[a[:20]], sampling_params={"max_new_tokens": 6, "temperature": 0, "ignore_eos": True})
+    assert len(outs[0]["output_ids"]) == 6
+    if dtype == "float32":
+        seq = list(a[:20])
+        for _ in range(6):
+            seq.append(int(h.oracle(seq)[-1].argmax()))
+        assert outs[0]["output_ids"] == seq[20:]
+    h.close()
