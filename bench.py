@@ -46,6 +46,10 @@ def parse_args():
     ap.add_argument("--disable-overlap", action="store_true")
     ap.add_argument("--comm-backend", default="auto")
     ap.add_argument("--quantization", default=None)
+    ap.add_argument("--hybrid-compare", action="store_true",
+                    help="instead of the default workload: Rirotar beside Qwen3-Next at equal size (engine prefill / decode) and its kernels beside "
+                         "the like ops, one JSON line per measurement (sglang_b200/benchmark/hybrid_compare.py)")
+    ap.add_argument("--hybrid-sizes", default="2048,4096", help="model widths of --hybrid-compare")
     return ap.parse_args()
 
 
@@ -190,6 +194,11 @@ def main() -> None:
         return
     if args.impl == "vllm":
         run_vllm(args)
+        return
+    if args.hybrid_compare:
+        from sglang_b200.benchmark.hybrid_compare import main as hybrid_main
+
+        hybrid_main(args.hybrid_sizes)
         return
     import numpy as np
     import torch

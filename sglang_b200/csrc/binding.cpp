@@ -273,8 +273,8 @@ void gated_delta_rule(const at::Tensor& u, int64_t Hk, int64_t Dk, int64_t H, in
 }
 
 void latent_attention(const at::Tensor& q, const at::Tensor& cache, int64_t rank, const at::Tensor& page_table, const at::Tensor& req_slots,
-                      const at::Tensor& seq_lens, c10::optional<at::Tensor> cu_q, int64_t max_q_len, int64_t page_size, double scale, int64_t window,
-                      c10::optional<at::Tensor> sinks, at::Tensor out) {
+                      const at::Tensor& seq_lens, c10::optional<at::Tensor> cu_q, int64_t max_q_len, int64_t max_kv_len, int64_t page_size, double scale,
+                      int64_t window, c10::optional<at::Tensor> sinks, at::Tensor out) {
   CHECK_CUDA(q); CHECK_I32(page_table); CHECK_I32(req_slots); CHECK_I32(seq_lens);
   TORCH_CHECK(q.scalar_type() == at::kFloat && q.dim() == 3 && q.is_contiguous() && out.scalar_type() == at::kFloat && out.is_contiguous() &&
               out.numel() == q.numel() && q.size(2) == rank);
@@ -285,11 +285,20 @@ void latent_attention(const at::Tensor& q, const at::Tensor& cache, int64_t rank
   if (sinks.has_value()) TORCH_CHECK(sinks->scalar_type() == at::kFloat && sinks->is_contiguous() && sinks->numel() == q.size(1));
   if (q.size(0) == 0) return;
   c10::cuda::CUDAGuard g(q.device());
+  // decode splits the keys of a request over CTAs: room for up to 32 partial results per (request, head)
+  const bool decode = !cu_q.has_value() || max_q_len == 1;
+  at::Tensor ws;
+  size_t ws_floats = 0;
+  if (decode) {
+    const int64_t ns = std::max<int64_t>(1, std::min<int64_t>(32, 296 / std::max<int64_t>(1, B)));
+    ws_floats = (size_t)(B * ns * q.size(1) * (rank + 2));
+    ws = at::empty({(int64_t)ws_floats}, q.options());
+  }
   sglb::latent_attention(q.data_ptr<float>(), cache.data_ptr(), cache.scalar_type() == at::kBFloat16, (int)cache.stride(0), (int)rank,
                          page_table.data_ptr<int>(), (int)page_table.stride(0), (int)page_size, req_slots.data_ptr<int>(), seq_lens.data_ptr<int>(),
-                         opt_ptr<int>(cu_q), B, (int)max_q_len, (int)q.size(1), (float)scale, (int)window, opt_ptr<float>(sinks),
-                         out.data_ptr<float>(), cur_stream());
-  count();
+                         opt_ptr<int>(cu_q), B, (int)max_q_len, (int)max_kv_len, (int)q.size(1), (float)scale, (int)window, opt_ptr<float>(sinks),
+                         out.data_ptr<float>(), decode ? ws.data_ptr<float>() : nullptr, ws_floats, cur_stream());
+  count(decode ? 2 : 1);
 }
 
 // bench tool: per-role cycle accounting of the decode attention kernel into buf [ctas * 30] (int64); an empty tensor turns it off
@@ -579,7 +588,7 @@ void moe_topk_softmax(const at::Tensor& logits, at::Tensor out_w, at::Tensor out
 void moe_grouped_mlp_impl(const at::Tensor& x, const at::Tensor& w13, const at::Tensor& w2, const at::Tensor& topk_w,
                           const at::Tensor& topk_ids, c10::optional<at::Tensor> out, int64_t expert_offset,
                           const int64_t* peer_slots, const int64_t* peer_flags, int rank, int world, const uint32_t* epoch,
-                          uint32_t* done) {
+                          uint32_t* done, int act = 0, float act_limit = 0.f, float act_alpha = 0.f) {
   CHECK_CUDA(x); CHECK_BF16(x); CHECK_BF16(w13); CHECK_BF16(w2); CHECK_I32(topk_ids); CHECK_LAST_CONTIG(x);
   TORCH_CHECK(x.dim() == 2 && w13.dim() == 3 && w2.dim() == 3 && w13.is_contiguous() && w2.is_contiguous());
   TORCH_CHECK(topk_w.scalar_type() == at::kFloat && topk_w.is_contiguous() && topk_ids.is_contiguous());
@@ -603,8 +612,17 @@ void moe_grouped_mlp_impl(const at::Tensor& x, const at::Tensor& w13, const at::
   auto xs = at::empty({cap, H}, x.options());
   sglb::moe_gather(x.data_ptr(), sorted_row, num_tiles, xs.data_ptr(), H, (int)x.stride(0), K, cap, num_sms(), stream);
   auto h = at::empty({cap, I}, x.options());
-  sglb::gemm_bf16_tc_grouped(xs.data_ptr(), w13.data_ptr(), h.data_ptr(), nullptr, cap, I, H, H, I, E, tile_expert, num_tiles, true,
-                             num_sms(), stream);
+  if (act == 0) {
+    sglb::gemm_bf16_tc_grouped(xs.data_ptr(), w13.data_ptr(), h.data_ptr(), nullptr, cap, I, H, H, I, E, tile_expert, num_tiles, true,
+                               num_sms(), stream);
+  } else {
+    // clamped GLU: the gate|up block comes out of the grouped GEMM whole, the activation is its own (vectorised) pass
+    auto h2 = at::empty({cap, 2 * I}, x.options());
+    sglb::gemm_bf16_tc_grouped(xs.data_ptr(), w13.data_ptr(), h2.data_ptr(), nullptr, cap, 2 * I, H, H, 2 * I, E, tile_expert, num_tiles, false,
+                               num_sms(), stream);
+    sglb::clamped_glu(h2.data_ptr(), h.data_ptr(), true, cap, I, act_limit, act_alpha, stream);
+    count();
+  }
   auto& ys = xs;   // the gathered inputs are dead once the first GEMM has run (same stream): reuse as the [cap, H] output
   sglb::gemm_bf16_tc_grouped(h.data_ptr(), w2.data_ptr(), ys.data_ptr(), row_w.data_ptr<float>(), cap, H, I, I, H, E, tile_expert,
                              num_tiles, false, num_sms(), stream);
@@ -621,6 +639,12 @@ void moe_grouped_mlp(const at::Tensor& x, const at::Tensor& w13, const at::Tenso
                      const at::Tensor& topk_ids, at::Tensor out, int64_t expert_offset) {
   CHECK_BF16(out);
   moe_grouped_mlp_impl(x, w13, w2, topk_w, topk_ids, out, expert_offset, nullptr, nullptr, 0, 1, nullptr, nullptr);
+}
+
+void moe_grouped_mlp_glu(const at::Tensor& x, const at::Tensor& w13, const at::Tensor& w2, const at::Tensor& topk_w,
+                         const at::Tensor& topk_ids, at::Tensor out, int64_t expert_offset, double limit, double alpha) {
+  CHECK_BF16(out);
+  moe_grouped_mlp_impl(x, w13, w2, topk_w, topk_ids, out, expert_offset, nullptr, nullptr, 0, 1, nullptr, nullptr, 1, (float)limit, (float)alpha);
 }
 
 void moe_grouped_mlp_push(const at::Tensor& x, const at::Tensor& w13, const at::Tensor& w2, const at::Tensor& topk_w,
@@ -652,6 +676,8 @@ TORCH_LIBRARY(sglb, m) {
   m.def("moe_topk_softmax(Tensor logits, Tensor(a!) out_w, Tensor(b!) out_ids, bool renorm) -> ()", &moe_topk_softmax);
   m.def("moe_grouped_mlp(Tensor x, Tensor w13, Tensor w2, Tensor topk_w, Tensor topk_ids, Tensor(a!) out, int expert_offset) -> ()",
         &moe_grouped_mlp);
+  m.def("moe_grouped_mlp_glu(Tensor x, Tensor w13, Tensor w2, Tensor topk_w, Tensor topk_ids, Tensor(a!) out, int expert_offset, float limit, "
+        "float alpha) -> ()", &moe_grouped_mlp_glu);
   m.def("moe_grouped_mlp_push(Tensor x, Tensor w13, Tensor w2, Tensor topk_w, Tensor topk_ids, int expert_offset, Tensor peer_slot_ptrs, "
         "Tensor peer_flag_ptrs, int rank, int world, Tensor(a!) epoch, Tensor(b!) done) -> ()", &moe_grouped_mlp_push);
   m.def("gemm_push(Tensor a, Tensor w, Tensor peer_slot_ptrs, Tensor peer_flag_ptrs, int rank, int world, Tensor(a!) epoch, "
@@ -691,7 +717,7 @@ TORCH_LIBRARY(sglb, m) {
         "Tensor req_slots, Tensor seq_lens, Tensor? cu_q, Tensor? gate_raw, Tensor? norm_w, float eps, bool gate_silu, bool per_channel, Tensor(b!) out) -> ()",
         &gated_delta_rule);
   m.def("latent_attention(Tensor q, Tensor cache, int rank, Tensor page_table, Tensor req_slots, Tensor seq_lens, Tensor? cu_q, int max_q_len, "
-        "int page_size, float scale, int window, Tensor? sinks, Tensor(a!) out) -> ()", &latent_attention);
+        "int max_kv_len, int page_size, float scale, int window, Tensor? sinks, Tensor(a!) out) -> ()", &latent_attention);
   m.def("gated_delta_update(Tensor(a!) state, Tensor req_slots, Tensor u, Tensor g, Tensor beta, int Hk, Tensor(b!) out) -> ()", &gated_delta_update);
   m.def("causal_conv1d(Tensor x, Tensor w, Tensor? bias, Tensor(a!) conv_state, Tensor? cu_q, Tensor req_slots, Tensor seq_lens, int max_q_len, "
         "bool silu, Tensor(b!) u) -> ()", &causal_conv1d);

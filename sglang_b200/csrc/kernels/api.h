@@ -110,8 +110,8 @@ bool gated_delta_rule(const float* u, int ldu, int Hk, int Dk, int H, int Dv, co
                       const int* req_slots, const int* seq_lens, const int* cu_q, int B, float* out, cudaStream_t stream);
 // latent_attention.cu
 void latent_attention(const float* q, const void* cache, bool cache_bf16, int ldc, int R, const int* page_table, int pt_stride, int page_size,
-                      const int* req_slots, const int* seq_lens, const int* cu_q, int B, int max_q_len, int H, float scale, int window,
-                      const float* sinks, float* out, cudaStream_t stream);
+                      const int* req_slots, const int* seq_lens, const int* cu_q, int B, int max_q_len, int max_kv_len, int H, float scale,
+                      int window, const float* sinks, float* out, float* workspace, size_t workspace_floats, cudaStream_t stream);
 void greedy_shard(const void* logits, bool bf16, int B, int stride, int v_valid, int v_offset, int rank, int tp, int b_pad, void* buf,
                   cudaStream_t stream);
 void greedy_merge(const void* buf, int tp, int b_pad, int B, const int* out_slots, int* next_token_buf, int* out_tokens, cudaStream_t stream);

@@ -31,15 +31,18 @@ struct LatentParams {
   const float* sinks;
   int H, R, HG, window;
   float scale;
+  int nsplit;                                  // decode only: the visible keys of a request are cut into nsplit ranges, one CTA each
+  float* part_o; float* part_ml;               // [T, nsplit, H, R] unnormalised outputs and [T, nsplit, H, 2] (running max, sum)
 };
 
-template <typename TCache, int QT>
+template <typename TCache, int QT, int PP>
 __global__ void __launch_bounds__(NW * 32) latent_attention_kernel(const LatentParams p) {
   extern __shared__ float sm[];
   const int b = blockIdx.y;
   const int qbase = p.cu_q ? p.cu_q[b] : b;
   const int n = p.cu_q ? p.cu_q[b + 1] - qbase : 1;
-  const int t0 = blockIdx.x * QT;
+  const int split = QT == 1 ? blockIdx.x : 0;          // decode: blockIdx.x is the key range, prompts: the query tile
+  const int t0 = QT == 1 ? 0 : blockIdx.x * QT;
   if (t0 >= n) return;
   const int nq = min(QT, n - t0);
   const int L = p.seq_lens[b];
@@ -65,12 +68,17 @@ __global__ void __launch_bounds__(NW * 32) latent_attention_kernel(const LatentP
 #pragma unroll
   for (int k = 0; k < PPW_MAX; ++k) {
     const int pr = warp + k * NW;
-    const float sink = (p.sinks && pr < P) ? p.sinks[h0 + pr % nh] : -INFINITY;
-    m_run[k] = sink;
-    l_run[k] = p.sinks ? 1.f : 0.f;
+    const bool sink_here = p.sinks && pr < P && split == 0;          // the sink is counted once: by the first key range
+    m_run[k] = sink_here ? p.sinks[h0 + pr % nh] : -INFINITY;
+    l_run[k] = sink_here ? 1.f : 0.f;
   }
-  const int last = pos0 + nq - 1;
-  const int first = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+  int last = pos0 + nq - 1;
+  int first = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+  if (QT == 1 && p.nsplit > 1) {
+    const int per = (last - first + p.nsplit) / p.nsplit;             // ceil((last - first + 1) / nsplit)
+    first += split * per;
+    last = min(last, first + per - 1);
+  }
   const int* pt = p.page_table + (size_t)p.req_slots[b] * p.pt_stride;
   const TCache* cache = (const TCache*)p.cache;
   for (int k0 = first; k0 <= last; k0 += KT) {
@@ -87,49 +95,79 @@ __global__ void __launch_bounds__(NW * 32) latent_attention_kernel(const LatentP
     }
     __syncthreads();
     const int kp = k0 + lane;
+    // the warp's pairs go four at a time: one latent value from shared memory feeds four score sums, one probability shuffle four columns
 #pragma unroll
-    for (int k = 0; k < PPW_MAX; ++k) {
-      const int pr = warp + k * NW;
-      if (pr >= P) break;
-      const int qi = pr / nh;
-      const int qpos = pos0 + qi;
-      const int lo = p.window > 0 ? qpos - p.window + 1 : 0;
-      if (k0 > qpos || k0 + KT - 1 < lo) continue;          // no key of this tile is visible to the pair (warp-uniform)
-      const bool vis = kp <= qpos && kp >= lo;
-      const float* qv = s_q + pr * R;
-      const float* cv = s_c + lane * RP;
-      float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-      int r = 0;
-      for (; r + 4 <= R; r += 4) {
-        a0 += qv[r] * cv[r];
-        a1 += qv[r + 1] * cv[r + 1];
-        a2 += qv[r + 2] * cv[r + 2];
-        a3 += qv[r + 3] * cv[r + 3];
+    for (int g0 = 0; g0 < PPW_MAX; g0 += PP) {
+      if (warp + g0 * NW >= P) break;
+      bool act[PP], vis[PP];
+      const float* qv[PP];
+      bool any = false;
+#pragma unroll
+      for (int u = 0; u < PP; ++u) {
+        const int pr = warp + (g0 + u) * NW;
+        const int qpos = pos0 + (pr < P ? pr / nh : 0);
+        const int lo = p.window > 0 ? qpos - p.window + 1 : 0;
+        act[u] = pr < P && !(k0 > qpos || k0 + KT - 1 < lo);          // some key of this tile is visible to the pair (warp-uniform)
+        vis[u] = act[u] && kp <= qpos && kp >= lo && kp <= last;          // (a decode key range may end inside the tile)
+        qv[u] = s_q + (pr < P ? pr : 0) * R;
+        any = any || act[u];
       }
-      for (; r < R; ++r) a0 += qv[r] * cv[r];
-      const float s = vis ? ((a0 + a1) + (a2 + a3)) * p.scale : -INFINITY;
-      const float m_new = fmaxf(m_run[k], warp_max(s));
-      if (m_new == -INFINITY) continue;
-      const float alpha = m_run[k] == -INFINITY ? 0.f : expf(m_run[k] - m_new);
-      const float pj = vis ? expf(s - m_new) : 0.f;
-      l_run[k] = l_run[k] * alpha + warp_sum(pj);
-      m_run[k] = m_new;
-      float* ov = s_o + pr * R;
-      for (int c0 = 0; c0 < R; c0 += 128) {                 // 4 column groups per pass: one shuffle feeds 4 multiply-adds
-        float acc[4] = {0.f, 0.f, 0.f, 0.f};
-        int cc[4];
+      if (!any) continue;
+      const float* cv = s_c + lane * RP;
+      float a[PP], a2[PP];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) cc[u] = min(c0 + 32 * u + lane, R - 1);
-#pragma unroll 8
+      for (int u = 0; u < PP; ++u) a[u] = a2[u] = 0.f;
+      int r = 0;
+      for (; r + 2 <= R; r += 2) {
+        const float c0 = cv[r], c1 = cv[r + 1];
+#pragma unroll
+        for (int u = 0; u < PP; ++u) {
+          a[u] += qv[u][r] * c0;
+          a2[u] += qv[u][r + 1] * c1;
+        }
+      }
+      if (r < R) {
+        const float c0 = cv[r];
+#pragma unroll
+        for (int u = 0; u < PP; ++u) a[u] += qv[u][r] * c0;
+      }
+      float pj[PP], alpha[PP];
+#pragma unroll
+      for (int u = 0; u < PP; ++u) {
+        pj[u] = 0.f;
+        alpha[u] = 1.f;
+        if (!act[u]) continue;
+        const int k = g0 + u;
+        const float sc = vis[u] ? (a[u] + a2[u]) * p.scale : -INFINITY;
+        const float m_new = fmaxf(m_run[k], warp_max(sc));
+        if (m_new == -INFINITY) { act[u] = false; continue; }
+        alpha[u] = m_run[k] == -INFINITY ? 0.f : expf(m_run[k] - m_new);
+        pj[u] = vis[u] ? expf(sc - m_new) : 0.f;
+        l_run[k] = l_run[k] * alpha[u] + warp_sum(pj[u]);
+        m_run[k] = m_new;
+      }
+      for (int c0 = 0; c0 < R; c0 += 64) {                  // two column groups per pass
+        float acc[PP][2];
+#pragma unroll
+        for (int u = 0; u < PP; ++u) acc[u][0] = acc[u][1] = 0.f;
+        const int cc0 = min(c0 + lane, R - 1), cc1 = min(c0 + 32 + lane, R - 1);
+#pragma unroll 4
         for (int j = 0; j < KT; ++j) {
-          const float pb = __shfl_sync(0xffffffffu, pj, j);
+          const float v0 = s_c[j * RP + cc0], v1 = s_c[j * RP + cc1];
 #pragma unroll
-          for (int u = 0; u < 4; ++u) acc[u] += pb * s_c[j * RP + cc[u]];
+          for (int u = 0; u < PP; ++u) {
+            const float pb = __shfl_sync(0xffffffffu, pj[u], j);
+            acc[u][0] += pb * v0;
+            acc[u][1] += pb * v1;
+          }
         }
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int c = c0 + 32 * u + lane;
-          if (c < R) ov[c] = ov[c] * alpha + acc[u];
+        for (int u = 0; u < PP; ++u) {
+          if (!act[u]) continue;
+          float* ov = s_o + (warp + (g0 + u) * NW) * R;
+          const int ca = c0 + lane, cb = c0 + 32 + lane;
+          if (ca < R) ov[ca] = ov[ca] * alpha[u] + acc[u][0];
+          if (cb < R) ov[cb] = ov[cb] * alpha[u] + acc[u][1];
         }
       }
     }
@@ -140,44 +178,102 @@ __global__ void __launch_bounds__(NW * 32) latent_attention_kernel(const LatentP
     const int pr = warp + k * NW;
     if (pr >= P) break;
     const int qi = pr / nh, hi = pr - qi * nh;
+    if (QT == 1 && p.nsplit > 1) {
+      const size_t row = ((size_t)(qbase + qi) * p.nsplit + split) * p.H + h0 + hi;
+      for (int c = lane; c < R; c += 32) p.part_o[row * R + c] = s_o[pr * R + c];
+      if (lane == 0) { p.part_ml[row * 2] = m_run[k]; p.part_ml[row * 2 + 1] = l_run[k]; }
+      continue;
+    }
     const float inv = 1.f / l_run[k];
     float* dst = p.out + ((size_t)(qbase + t0 + qi) * p.H + h0 + hi) * R;
     for (int c = lane; c < R; c += 32) dst[c] = s_o[pr * R + c] * inv;
   }
 }
 
+// decode, nsplit > 1: out[t, h, :] = sum_s o_s exp(m_s - m) / sum_s l_s exp(m_s - m); one warp per (token, head)
+__global__ void __launch_bounds__(128) latent_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, float* __restrict__ out,
+                                                           int rows, int H, int R, int nsplit) {
+  const int row = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const int t = row / H, h = row - t * H;
+  float m = -INFINITY;
+  for (int s = 0; s < nsplit; ++s) m = fmaxf(m, part_ml[(((size_t)t * nsplit + s) * H + h) * 2]);
+  float l = 0.f;
+  for (int s = 0; s < nsplit; ++s) {
+    const float* ml = part_ml + (((size_t)t * nsplit + s) * H + h) * 2;
+    if (ml[0] != -INFINITY) l += ml[1] * expf(ml[0] - m);
+  }
+  const float inv = 1.f / l;
+  for (int c = lane; c < R; c += 32) {
+    float acc = 0.f;
+    for (int s = 0; s < nsplit; ++s) {
+      const size_t pr = ((size_t)t * nsplit + s) * H + h;
+      const float ms = part_ml[pr * 2];
+      if (ms != -INFINITY) acc += part_o[pr * R + c] * expf(ms - m);
+    }
+    out[(size_t)row * R + c] = acc * inv;
+  }
+}
+
+template <typename TCache, int QT, int PP>
+void launch_pp(const LatentParams& p, dim3 grid, size_t smem, cudaStream_t stream) {
+  auto kern = latent_attention_kernel<TCache, QT, PP>;
+  if (smem > 48 * 1024) SGLB_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  kern<<<grid, NW * 32, smem, stream>>>(p);
+  SGLB_CUDA_CHECK(cudaGetLastError());
+}
+
 template <typename TCache, int QT>
-void launch(LatentParams p, int B, int max_q_len, cudaStream_t stream) {
+void launch(LatentParams p, int B, int max_q_len, int max_kv_len, float* workspace, size_t workspace_floats, cudaStream_t stream) {
   // heads per CTA: as many as fit 200 KB next to the key tile, at most 16 pairs per warp
   const size_t tile = (size_t)KT * (p.R + 1) * 4 + KT * 4;
   const size_t per_head = (size_t)QT * p.R * 4 * 2;
   int hg = (int)std::min<size_t>((size_t)p.H, (200 * 1024 - tile) / per_head);
   hg = std::min(hg, 16 * NW / QT);
   if (hg < 1) throw std::runtime_error("sglb latent_attention: latent rank too large for one CTA");
+  const int hgroups = (p.H + hg - 1) / hg;
   p.HG = hg;
+  p.nsplit = 1;
+  if (QT == 1) {
+    // decode has few queries: cut every request's visible keys into ranges (>= 64 keys each) until ~2 CTAs per SM are in flight
+    const int span = p.window > 0 ? std::min(p.window, max_kv_len) : max_kv_len;
+    int ns = std::min(std::min(296 / std::max(1, B * hgroups), span / 64), 32);
+    ns = std::max(ns, 1);
+    if ((size_t)B * ns * p.H * (p.R + 2) > workspace_floats) ns = 1;
+    p.nsplit = ns;
+    p.part_o = workspace;
+    p.part_ml = workspace + (size_t)B * ns * p.H * p.R;
+  }
   const size_t smem = tile + per_head * hg;
-  auto kern = latent_attention_kernel<TCache, QT>;
-  if (smem > 48 * 1024) SGLB_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  dim3 grid((max_q_len + QT - 1) / QT, B, (p.H + hg - 1) / hg);
-  kern<<<grid, NW * 32, smem, stream>>>(p);
-  SGLB_CUDA_CHECK(cudaGetLastError());
+  dim3 grid(QT == 1 ? p.nsplit : (max_q_len + QT - 1) / QT, B, hgroups);
+  const int ppw = (QT * hg + NW - 1) / NW;               // pairs per warp: group them 4, 2 or 1 at a time
+  if (ppw >= 3) launch_pp<TCache, QT, 4>(p, grid, smem, stream);
+  else if (ppw == 2) launch_pp<TCache, QT, 2>(p, grid, smem, stream);
+  else launch_pp<TCache, QT, 1>(p, grid, smem, stream);
+  if (QT == 1 && p.nsplit > 1) {
+    const int rows = B * p.H;
+    latent_merge_kernel<<<(rows + 3) / 4, 128, 0, stream>>>(p.part_o, p.part_ml, p.out, rows, p.H, p.R, p.nsplit);
+    SGLB_CUDA_CHECK(cudaGetLastError());
+  }
 }
 
 }  // namespace
 
 void latent_attention(const float* q, const void* cache, bool cache_bf16, int ldc, int R, const int* page_table, int pt_stride, int page_size,
-                      const int* req_slots, const int* seq_lens, const int* cu_q, int B, int max_q_len, int H, float scale, int window,
-                      const float* sinks, float* out, cudaStream_t stream) {
+                      const int* req_slots, const int* seq_lens, const int* cu_q, int B, int max_q_len, int max_kv_len, int H, float scale,
+                      int window, const float* sinks, float* out, float* workspace, size_t workspace_floats, cudaStream_t stream) {
   if (B <= 0 || max_q_len <= 0) return;
   if (B > 65535) throw std::runtime_error("sglb latent_attention: more than 65535 requests in one call");
   LatentParams p;
   p.q = q; p.out = out; p.cache = cache; p.ldc = ldc; p.page_table = page_table; p.pt_stride = pt_stride; p.page_size = page_size;
-  p.req_slots = req_slots; p.seq_lens = seq_lens; p.cu_q = cu_q; p.sinks = sinks; p.H = H; p.R = R; p.HG = 1; p.window = window; p.scale = scale;
+  p.req_slots = req_slots; p.seq_lens = seq_lens; p.cu_q = cu_q; p.sinks = sinks; p.H = H; p.R = R; p.HG = 1; p.window = window; p.scale = scale; p.nsplit = 1; p.part_o = nullptr; p.part_ml = nullptr;
   const bool decode = cu_q == nullptr || max_q_len == 1;
   if (cache_bf16) {
-    if (decode) launch<__nv_bfloat16, 1>(p, B, 1, stream); else launch<__nv_bfloat16, 8>(p, B, max_q_len, stream);
+    if (decode) launch<__nv_bfloat16, 1>(p, B, 1, max_kv_len, workspace, workspace_floats, stream);
+    else launch<__nv_bfloat16, 8>(p, B, max_q_len, max_kv_len, workspace, workspace_floats, stream);
   } else {
-    if (decode) launch<float, 1>(p, B, 1, stream); else launch<float, 8>(p, B, max_q_len, stream);
+    if (decode) launch<float, 1>(p, B, 1, max_kv_len, workspace, workspace_floats, stream);
+    else launch<float, 8>(p, B, max_q_len, max_kv_len, workspace, workspace_floats, stream);
   }
 }
 

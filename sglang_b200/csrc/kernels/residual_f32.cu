@@ -62,6 +62,24 @@ __global__ void __launch_bounds__(256) clamped_glu_kernel(const T* __restrict__ 
   stf<T>(out + (size_t)blockIdx.x * I + i, g / (1.f + expf(-alpha * g)) * (u + 1.f));
 }
 
+// 16-byte lanes: 8 bf16 gate values and the 8 matching up values per thread
+__global__ void __launch_bounds__(256) clamped_glu_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int I,
+                                                                 float limit, float alpha) {
+  const int i = (blockIdx.y * 256 + threadIdx.x) * 8;
+  if (i >= I) return;
+  const __nv_bfloat16* row = gu + (size_t)blockIdx.x * 2 * I;
+  const U4 g = ldg128(row + i), u = ldg128(row + I + i);
+  const uint32_t gw[4] = {g.x, g.y, g.z, g.w}, uw[4] = {u.x, u.y, u.z, u.w};
+  uint32_t o[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const float g0 = fminf(bf16_lo(gw[k]), limit), g1 = fminf(bf16_hi(gw[k]), limit);
+    const float u0 = fminf(fmaxf(bf16_lo(uw[k]), -limit), limit), u1 = fminf(fmaxf(bf16_hi(uw[k]), -limit), limit);
+    o[k] = pack_bf16(g0 / (1.f + __expf(-alpha * g0)) * (u0 + 1.f), g1 / (1.f + __expf(-alpha * g1)) * (u1 + 1.f));
+  }
+  st128(out + (size_t)blockIdx.x * I + i, U4{o[0], o[1], o[2], o[3]});
+}
+
 }  // namespace
 
 void add_rmsnorm_f32(float* residual, const void* delta, bool delta_bf16, const void* w, void* out, bool out_bf16, int T, int H, float eps,
@@ -88,6 +106,11 @@ void clamped_glu(const void* gu, void* out, bool bf16, int T, int I, float limit
   if (T <= 0 || I <= 0) return;
   if ((I + 255) / 256 > 65535) throw std::runtime_error("sglb clamped_glu: feed-forward width too large for one launch");
   dim3 g(T, (I + 255) / 256);
+  if (bf16 && I % 8 == 0 && ((uintptr_t)gu % 16) == 0 && ((uintptr_t)out % 16) == 0) {
+    clamped_glu_bf16x8_kernel<<<dim3(T, (I / 8 + 255) / 256), 256, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, I, limit, alpha);
+    SGLB_CUDA_CHECK(cudaGetLastError());
+    return;
+  }
   if (bf16)
     clamped_glu_kernel<__nv_bfloat16><<<g, 256, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, I, limit, alpha);
   else

@@ -85,6 +85,6 @@ class WindowedLatentAttention(nn.Module):
         uk, uv = self._absorbed()
         q_lat = torch.bmm(qc[:, :hd].float().view(T, self.H, self.D).transpose(0, 1), uk).transpose(0, 1).contiguous()      # [T, H, R]
         o_lat = ops.latent_attention(q_lat, cache, self.R, fb.page_table, fb.req_slots, fb.seq_lens, fb.cu_q, fb.q_lens, fb.max_q_len, fb.page_size,
-                                     self.attn.scale, self.attn.window, self.sinks)
+                                     self.attn.scale, self.attn.window, self.sinks, fb.max_kv_len)
         o = torch.bmm(o_lat.transpose(0, 1), uv).transpose(0, 1).reshape(T, self.H * self.Dv)
         return ops.linear(o.to(h.dtype), self.o_weight)

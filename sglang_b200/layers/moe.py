@@ -72,7 +72,7 @@ class FusedMoE(nn.Module):
         self.inter_local = intermediate_size // self.moe_tp
         self.w13 = nn.Parameter(torch.zeros(self.local_experts, 2 * self.inter_local, hidden_size, dtype=dtype), requires_grad=False)
         self.w2 = nn.Parameter(torch.zeros(self.local_experts, hidden_size, self.inter_local, dtype=dtype), requires_grad=False)
-        self.act = None          # None = silu(gate) * up; else a callable on the [rows, 2I] gate|up block (clamped GLU: models/rirotar.py)
+        self.act = None          # None = silu(gate) * up; ("clamped_glu", limit, alpha) = the clamped GLU (ops/moe_ops.py fused_moe)
         self.expert_load = None  # EPLB recorder hook
         self.placement = None    # eplb/placement.py ExpertPlacement once experts are replicated / moved; None = contiguous default
         self.rep_table = self.rep_count = None

@@ -285,6 +285,10 @@ class Qwen3NextForCausalLM(NemotronHForCausalLM):
             h = blk(h, fb)
         return m.norm(h)
 
+    def dummy_checkpoint(self, cfg: ModelConfig, device, dtype, seed: int = 0, scale: float = 0.02):
+        """no synthetic checkpoint of its own: every parameter takes the loader's name-seeded random init (throughput runs)"""
+        return iter(())
+
     def make_mamba_pool(self, slots: int, device) -> Optional[MambaPool]:
         la = next((b.linear_attn for b in self.model.all_layers if b.kind == "mamba"), None)
         return None if la is None else MambaPool(self.model.num_mamba, slots, la.conv_dim, la.k, la.Hv, la.Dk, la.Dv, _DT[self.cfg.dtype], device)

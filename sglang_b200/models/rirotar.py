@@ -83,8 +83,7 @@ class GroupRoutedMoE(nn.Module):
         self.limit = float(mlp["expert"]["limit"])
         self.router = nn.Parameter(torch.zeros(self.E, width, dtype=dtype), requires_grad=False)
         self.experts = FusedMoE(self.E, self.top, width, int(mlp["expert"]["ff"]), dtype, True, 1, None, layer_id)
-        limit = self.limit
-        self.experts.act = lambda gu: ops.clamped_glu(gu.contiguous(), limit, GLU_ALPHA)
+        self.experts.act = ("clamped_glu", self.limit, GLU_ALPHA)
         self._router32 = None
 
     def load(self, leaf: str, w: torch.Tensor) -> bool:

@@ -460,13 +460,15 @@ def clamped_glu(gu: torch.Tensor, limit: float, alpha: float = 1.702) -> torch.T
 
 def latent_attention(q_lat: torch.Tensor, cache: torch.Tensor, rank: int, page_table: torch.Tensor, req_slots: torch.Tensor, seq_lens: torch.Tensor,
                      cu_q: Optional[torch.Tensor], q_lens: Optional[torch.Tensor], max_q_len: int, page_size: int, scale: float, window: int = -1,
-                     sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
+                     sinks: Optional[torch.Tensor] = None, max_kv_len: int = 0) -> torch.Tensor:
     """absorbed multi-query attention over a paged cache of latent rows with a sliding window and per-head sinks
-    (csrc/kernels/latent_attention.cu; contract in ``torch_ref.latent_attention``).  ``cu_q`` None = one query per request."""
+    (csrc/kernels/latent_attention.cu; contract in ``torch_ref.latent_attention``).  ``cu_q`` None = one query per request.
+    ``max_kv_len`` (host-side longest sequence; 0 = unknown) only steers how decode splits the keys over CTAs."""
     if _use_native(q_lat) and q_lat.dtype == torch.float32 and cache.dtype in (torch.bfloat16, torch.float32) and q_lat.is_contiguous():
         out = torch.empty_like(q_lat)
-        torch.ops.sglb.latent_attention(q_lat, cache, int(rank), page_table, req_slots, seq_lens, cu_q, int(max_q_len), int(page_size),
-                                        float(scale), int(window), sinks, out)
+        torch.ops.sglb.latent_attention(q_lat, cache, int(rank), page_table, req_slots, seq_lens, cu_q, int(max_q_len),
+                                        int(max_kv_len) if max_kv_len else (int(window) if window > 0 else 4096), int(page_size), float(scale),
+                                        int(window), sinks, out)
         return out
     return torch_ref.latent_attention(q_lat, cache, rank, page_table, req_slots, seq_lens, q_lens, page_size, scale, window, sinks)
 

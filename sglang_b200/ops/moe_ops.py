@@ -30,14 +30,28 @@ def topk_softmax(router_logits: torch.Tensor, top_k: int, renormalize: bool = Tr
 
 def fused_moe(x: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, topk_w: torch.Tensor, topk_ids: torch.Tensor,
               expert_offset: int = 0, act=None) -> torch.Tensor:
-    """``act``: None = silu(gate) * up, else a callable on the [rows, 2I] gate|up block (e.g. the clamped GLU of ``ops.clamped_glu``)"""
+    """``act``: None = silu(gate) * up; ``("clamped_glu", limit, alpha)`` = min(g, limit) * sigmoid(alpha g) * (clamp(u, +-limit) + 1)"""
+    fn = None
+    if act is not None:
+        kind, limit, alpha = act
+        assert kind == "clamped_glu", kind
+        from . import clamped_glu
+
+        fn = lambda gu: clamped_glu(gu.contiguous(), limit, alpha)
     if not x.is_cuda:
-        return torch_ref.fused_moe(x, w13, w2, topk_w, topk_ids, expert_offset, act)
+        return torch_ref.fused_moe(x, w13, w2, topk_w, topk_ids, expert_offset, fn)
+    H, I = x.shape[1], w2.shape[2]
+    if (act is not None and x.dtype == torch.bfloat16 and _has("moe_grouped_mlp_glu") and H % 32 == 0 and I % 16 == 0 and x.stride(1) == 1
+            and x.stride(0) % 8 == 0):
+        # expert-sorted rows through the tcgen05 grouped GEMMs, no host sync: align -> gather -> gate|up GEMM -> clamped GLU -> down GEMM -> combine
+        out = torch.empty_like(x)
+        torch.ops.sglb.moe_grouped_mlp_glu(x, w13, w2, topk_w, topk_ids, out, expert_offset, float(limit), float(alpha))
+        return out
     if act is None and x.dtype == torch.bfloat16 and _has("moe_grouped_mlp"):
         out = torch.empty_like(x)
         torch.ops.sglb.moe_grouped_mlp(x, w13, w2, topk_w, topk_ids, out, expert_offset)
         return out
-    return _fused_moe_sorted(x, w13, w2, topk_w, topk_ids, expert_offset, act)
+    return _fused_moe_sorted(x, w13, w2, topk_w, topk_ids, expert_offset, fn)
 
 
 def _fused_moe_sorted(x, w13, w2, topk_w, topk_ids, expert_offset, act=None):
