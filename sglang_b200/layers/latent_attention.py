@@ -12,12 +12,19 @@ so the paged cache holds ``kv_rank`` values per token and layer and the kernel i
 (``ops.latent_attention``, csrc/kernels/latent_attention.cu: one kernel for prompt portions and single decode tokens).  The soft-max, the
 latent norm and both absorbed products are fp32; the cache is in the model dtype.
 
+Prompt portions of bf16 models whose key and value heads are both 128 wide take the expanded route instead: the latent rows a portion can
+see (its own tokens and the window before them) are gathered once per forward, up-projected to per-head keys and values by one GEMM each
+into a scratch paged buffer, and the framework's tcgen05 flash-attention kernel runs over them with the same window; the sink enters
+through the log-sum-exp (``o * sigmoid(lse - sink)``).  Per (query, key, head) that costs ``dim + vdim`` multiply-adds on tensor cores
+instead of ``2 * kv_rank`` on CUDA cores.  Decode, fp32 serving and every other head size stay on the absorbed kernel.
+
 The window only masks: pages of tokens that left the window are still held until the request ends (the pool is sized by live tokens).
 """
 from __future__ import annotations
 
 from typing import Optional
 
+import numpy as np
 import torch
 from torch import nn
 
@@ -75,6 +82,54 @@ class WindowedLatentAttention(nn.Module):
             self._uv32 = self.uv.detach().float().view(self.H, self.Dv, self.R).transpose(1, 2).contiguous()  # [H, R, Dv]
         return self._uk32, self._uv32
 
+    EXPAND_PAGE = 64
+    expand_prefill = True            # class-wide switch of the expanded prompt route (tests compare it with the absorbed kernel)
+
+    def _expand_plan(self, fb: ForwardBatch):
+        """which cached rows this forward's prompt portions can see, laid out as a scratch paged buffer (built once per forward and window
+        on the host from the lengths the scheduler already holds; shared by all layers with that window)"""
+        plans = fb.__dict__.setdefault("_latent_expand", {})
+        W = self.attn.window
+        if W in plans:
+            return plans[W]
+        ps, P = fb.page_size, self.EXPAND_PAGE
+        sl, ql, slots = np.asarray(fb.seq_lens_cpu, dtype=np.int64), np.asarray(fb.q_lens_cpu, dtype=np.int64), fb.req_slots
+        lo = np.maximum(0, sl - ql - W + 1) if W > 0 else np.zeros_like(sl)
+        n = sl - lo
+        pages = (n + P - 1) // P
+        first = np.concatenate([[0], np.cumsum(pages)[:-1]]) + 1                      # (page 0 stays unused, like in the real pool)
+        B = len(sl)
+        pt = np.zeros((B, int(pages.max())), dtype=np.int32)
+        req = np.repeat(np.arange(B), n)
+        rel = np.concatenate([np.arange(k) for k in n])
+        for b in range(B):
+            pt[b, : pages[b]] = first[b] + np.arange(pages[b])
+        dev = fb.seq_lens.device
+        to = lambda a, dt: torch.from_numpy(np.ascontiguousarray(a)).to(dev, non_blocking=True).to(dt)
+        pos = to(lo[req] + rel, torch.int64)
+        reqd = to(req, torch.int64)
+        src = fb.page_table[slots.long()[reqd], pos // ps].long() * ps + pos % ps           # rows of the latent cache
+        dst = to((first[req] * P + rel), torch.int64)                                       # rows of the scratch buffer
+        plan = {"src": src, "dst": dst, "rows": int((first[-1] + pages[-1]) * P), "pt": to(pt, torch.int32), "n": to(n, torch.int32),
+                "slots": torch.arange(B, dtype=torch.int32, device=dev), "max_n": int(n.max())}
+        plans[W] = plan
+        return plan
+
+    def _forward_expanded(self, q: torch.Tensor, cache: torch.Tensor, fb: ForwardBatch) -> torch.Tensor:
+        T, H, D = q.shape[0], self.H, self.D
+        pl = self._expand_plan(fb)
+        c = cache[pl["src"], 0, : self.R]                                                   # [N, R] visible latent rows
+        kbuf = torch.zeros(pl["rows"], H, D, dtype=q.dtype, device=q.device)
+        vbuf = torch.zeros(pl["rows"], H, self.Dv, dtype=q.dtype, device=q.device)
+        kbuf[pl["dst"]] = ops.linear(c, self.uk).view(-1, H, D)
+        vbuf[pl["dst"]] = ops.linear(c, self.uv).view(-1, H, self.Dv)
+        lse = torch.empty(T, H, dtype=torch.float32, device=q.device) if self.sinks is not None else None
+        o = ops.paged_attention(q.view(T, H, D), kbuf, vbuf, pl["pt"], pl["slots"], pl["n"], fb.cu_q, fb.q_lens, fb.max_q_len, self.EXPAND_PAGE,
+                                self.attn.scale, causal=True, window=self.attn.window, lse=lse)
+        if lse is not None:
+            o = (o.float() * torch.sigmoid(lse - self.sinks[None, :]).unsqueeze(-1)).to(o.dtype)
+        return o.reshape(T, H * self.Dv)
+
     def forward(self, h: torch.Tensor, fb: ForwardBatch) -> torch.Tensor:
         T = h.shape[0]
         hd = self.H * self.D
@@ -82,6 +137,9 @@ class WindowedLatentAttention(nn.Module):
         c = ops.rmsnorm(qc[:, hd:].contiguous(), self.latent_norm, self.eps)
         cache = fb.kv_pool.k(self.attn.layer_id)                          # [slots, 1, cache_width]
         cache[fb.out_cache_loc.long(), 0, : self.R] = c.to(cache.dtype)
+        if (self.expand_prefill and fb.cu_q is not None and fb.max_q_len > 1 and h.is_cuda and h.dtype == torch.bfloat16 and self.D == 128 and self.Dv == 128
+                and fb.q_lens_cpu is not None and ops.native_available() and ops.attn_impl() == 0):
+            return ops.linear(self._forward_expanded(qc[:, :hd].contiguous(), cache, fb), self.o_weight)
         uk, uv = self._absorbed()
         q_lat = torch.bmm(qc[:, :hd].float().view(T, self.H, self.D).transpose(0, 1), uk).transpose(0, 1).contiguous()      # [T, H, R]
         o_lat = ops.latent_attention(q_lat, cache, self.R, fb.page_table, fb.req_slots, fb.seq_lens, fb.cu_q, fb.q_lens, fb.max_q_len, fb.page_size,

@@ -188,3 +188,41 @@ def test_engine_on_cuda_against_the_oracle(tmp_path, dtype, tol):
             seq.append(int(h.oracle(seq)[-1].argmax()))
         assert outs[0]["output_ids"] == seq[20:]
     h.close()
+
+
+def test_expanded_prompt_route_for_128_wide_heads_matches_the_absorbed_kernel(tmp_path):
+    """bf16 prompts with 128-wide key and value heads run the tcgen05 flash-attention kernel over up-projected keys and values; the result
+    has to agree with the absorbed latent kernel (same engine, route switched off) and with the oracle, for whole prompts, portions that
+    start inside the window, and a batch of unequal requests"""
+    import numpy as np
+
+    from sglang_b200.layers.latent_attention import WindowedLatentAttention as WLA
+    from test_rirotar import L, Harness, _attn, _cfg, _delta, _dense, _tokens
+
+    cfg = _cfg([L(_attn(heads=2, dim=128, vdim=128, kv_rank=64, window=50, scale=128 ** -0.5), _dense(ff=64)),
+                L(_delta("delta", heads=2, kv_heads=1, dim=16, vdim=16), None),
+                L(_attn(heads=3, dim=128, vdim=128, kv_rank=40, window=300, scale=128 ** -0.5), None)], width=64, vocab=96)
+    h = Harness(tmp_path, cfg, seed=4, device="cuda", dtype="bfloat16", page=16, max_tokens=2048)
+    a, b = _tokens(333, 96, 1), _tokens(120, 96, 2)
+    rms = lambda x, y: float(np.quantile(np.sqrt(((x - y) ** 2).mean(-1)), 0.9))
+
+    def run():
+        whole = h.step([("w", a, range(len(a)))], ["w"])
+        cut = h.run_cut("c", a, [70, 3, 130, 64, 60])
+        o1 = h.step([("x", a[:200], range(200)), ("y", b[:7], range(7))])
+        o2 = h.step([("x", a[200:], range(133)), ("y", b[7:], range(113))], ["x", "y"])
+        return whole, cut, np.concatenate([o1[:200], o2[:133]]), np.concatenate([o1[200:], o2[133:]])
+
+    assert WLA.expand_prefill
+    got = run()
+    WLA.expand_prefill = False
+    try:
+        ref = run()
+    finally:
+        WLA.expand_prefill = True
+    for x, y in zip(got, ref):
+        assert rms(x, y) < 0.05
+    ra, rb = h.oracle(a), h.oracle(b)
+    for x, y in zip(got, (ra, ra, ra, rb)):
+        assert rms(x, y) < 0.06
+    h.close()
