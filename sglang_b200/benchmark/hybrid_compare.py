@@ -193,6 +193,25 @@ def _kernel_numbers(timer: _Timer, hbm_gbs: float) -> List[dict]:
         nbytes = q.numel() * 4 * 2 + B * min(S, W + Q) * R * 2
         rec("latent_attention", "prefill" if Q > 1 else "decode", f"B{B} S{S} q{Q} H{H} R{R} window{W}", ms, nbytes,
             "deepseek latent path (torch_ref.paged_attention, no window)", like)
+        if Q > 1:          # the route bf16 prompts with 128-wide heads take: up-projection GEMMs + tcgen05 flash attention over the window rows
+            import types
+
+            from ..layers.latent_attention import WindowedLatentAttention
+
+            layer = WindowedLatentAttention(4096, H, 128, 128, R, 128 ** -0.5, W, 1e-6, 0, torch.bfloat16).to(dev)
+            for prm in (layer.uk, layer.uv):
+                prm.data.normal_(0.0, 0.03)
+            fb = types.SimpleNamespace(page_size=ps, seq_lens_cpu=[S] * B, q_lens_cpu=[Q] * B, req_slots=slots, page_table=pt, seq_lens=sl, cu_q=cu,
+                                       q_lens=ql, max_q_len=Q)
+            q128 = torch.randn(B * Q, H * 128, device=dev, generator=g).to(torch.bfloat16)
+
+            def expanded():
+                fb.__dict__.pop("_latent_expand", None)
+                layer._forward_expanded(q128, cache, fb)
+
+            ms2 = timer(expanded)
+            rec("latent_attention (expanded: GEMMs + tcgen05 flash attention)", "prefill", f"B{B} S{S} q{Q} H{H} D128 R{R} window{W}", ms2, nbytes,
+                "deepseek latent path (torch_ref.paged_attention, no window)", like)
     # ---- elementwise
     T, Wd = 8192, 4096
     res, d16 = torch.randn(T, Wd, device=dev), torch.randn(T, Wd, device=dev).to(torch.bfloat16)

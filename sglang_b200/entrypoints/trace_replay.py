@@ -45,6 +45,10 @@ def main(argv=None) -> int:
     from .engine import Engine
 
     device = ns.device if ns.device != "auto" else ("cuda" if torch.cuda.is_available() else "cpu")
+    from .. import build as _build
+
+    if not list(_build.ROOT.glob("sglb_rt*.so")):          # fresh checkout: the C++ host runtime (page allocator, radix tree) first
+        _build.build_runtime()
     if device == "cuda":
         from .. import ops
 
