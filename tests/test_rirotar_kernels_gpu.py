@@ -226,3 +226,26 @@ def test_expanded_prompt_route_for_128_wide_heads_matches_the_absorbed_kernel(tm
     for x, y in zip(got, (ra, ra, ra, rb)):
         assert rms(x, y) < 0.06
     h.close()
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", 3e-4), ("bfloat16", 0.1)])
+def test_engine_on_cuda_with_sizes_no_vector_lane_divides(tmp_path, dtype, tol):
+    """widths, ranks, head sizes, expert sizes and a vocabulary that are multiples of nothing convenient: every op has to take its general path"""
+    import numpy as np
+
+    from test_rirotar import L, Harness, _attn, _cfg, _delta, _dense, _moe, _tokens
+
+    cfg = _cfg([L(_attn(heads=5, dim=24, vdim=40, kv_rank=36, window=9, scale=0.3), _moe(experts=6, top=3, count=2, keep=1, ff=20)),
+                L(_delta("channel_delta", heads=3, kv_heads=1, dim=20, vdim=12, conv=2, rank=5), _dense(ff=100)),
+                L(_delta("delta", heads=2, kv_heads=2, dim=72, vdim=36, conv=7), None),
+                L(_attn(heads=1, dim=10, vdim=6, kv_rank=14, window=400, scale=0.9), _dense(ff=36))], width=100, vocab=301, softcap=0.0)
+    h = Harness(tmp_path, cfg, seed=21, device="cuda", dtype=dtype, page=16, max_tokens=1024)
+    a = _tokens(130, 301, 3)
+    ra = h.oracle(a)
+    if dtype == "float32":
+        err = lambda x, y: float(np.abs(x - y).max())
+    else:
+        err = lambda x, y: float(np.quantile(np.sqrt(((x - y) ** 2).mean(-1)), 0.5))
+    assert err(h.step([("w", a, range(len(a)))], ["w"]), ra) < tol
+    assert err(h.run_cut("c", a, [3, 40, 2, 17]), ra) < tol
+    h.close()
