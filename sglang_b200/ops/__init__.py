@@ -464,13 +464,25 @@ def latent_attention(q_lat: torch.Tensor, cache: torch.Tensor, rank: int, page_t
     """absorbed multi-query attention over a paged cache of latent rows with a sliding window and per-head sinks
     (csrc/kernels/latent_attention.cu; contract in ``torch_ref.latent_attention``).  ``cu_q`` None = one query per request.
     ``max_kv_len`` (host-side longest sequence; 0 = unknown) only steers how decode splits the keys over CTAs."""
-    if _use_native(q_lat) and q_lat.dtype == torch.float32 and cache.dtype in (torch.bfloat16, torch.float32) and q_lat.is_contiguous():
+    if (_use_native(q_lat) and q_lat.dtype == torch.float32 and cache.dtype in (torch.bfloat16, torch.float32) and q_lat.is_contiguous()
+            and rank <= 1024 and req_slots.numel() <= 65535):          # (a key tile and one head's accumulators have to fit shared memory)
         out = torch.empty_like(q_lat)
         torch.ops.sglb.latent_attention(q_lat, cache, int(rank), page_table, req_slots, seq_lens, cu_q, int(max_q_len),
                                         int(max_kv_len) if max_kv_len else (int(window) if window > 0 else 4096), int(page_size), float(scale),
                                         int(window), sinks, out)
         return out
     return torch_ref.latent_attention(q_lat, cache, rank, page_table, req_slots, seq_lens, q_lens, page_size, scale, window, sinks)
+
+
+def _delta_shape_ok(Dk: int, Dv: int) -> bool:
+    """the kernel keeps a column of the state in 1..16 lanes of 16, 32 or 64 rows each, one CTA (<= 512 or 1024 threads) per head"""
+    for rows, max_threads in ((32, 512), (16, 1024), (64, 512)):
+        ks = 1
+        while ks * rows < Dk and ks < 16:
+            ks <<= 1
+        if ks * rows >= Dk and Dv * ks <= max_threads:
+            return True
+    return False
 
 
 def gated_delta_rule(u: torch.Tensor, Hk: int, Dk: int, H: int, Dv: int, a_raw: torch.Tensor, A_log: torch.Tensor, dt_bias: torch.Tensor,
@@ -482,7 +494,8 @@ def gated_delta_rule(u: torch.Tensor, Hk: int, Dk: int, H: int, Dv: int, a_raw: 
     (csrc/kernels/delta_rule.cu; contract in ``torch_ref.gated_delta_rule``)."""
     if per_channel is None:
         per_channel = a_raw.shape[1] != H
-    if _use_native(u) and u.dtype == torch.float32 and state.dtype == torch.float32 and u.is_contiguous():
+    if (_use_native(u) and u.dtype == torch.float32 and state.dtype == torch.float32 and u.is_contiguous() and _delta_shape_ok(Dk, Dv)
+            and req_slots.numel() <= 65535):
         T = u.shape[0]
         out = torch.empty(T, H, Dv, dtype=torch.float32, device=u.device)
         f = lambda t: None if t is None else t.float().contiguous()

@@ -249,3 +249,25 @@ def test_engine_on_cuda_with_sizes_no_vector_lane_divides(tmp_path, dtype, tol):
     assert err(h.step([("w", a, range(len(a)))], ["w"]), ra) < tol
     assert err(h.run_cut("c", a, [3, 40, 2, 17]), ra) < tol
     h.close()
+
+
+@pytest.mark.parametrize("H,I,E,K,T", [(256, 64, 8, 4, 300), (64, 16, 3, 1, 50), (96, 48, 5, 3, 129), (32, 32, 2, 2, 1), (128, 80, 16, 4, 1000)])
+def test_clamped_glu_experts_grouped_against_the_per_expert_loop(H, I, E, K, T):
+    """expert-sorted rows through the grouped tcgen05 GEMMs with the clamped GLU between them == one GEMM pair per expert"""
+    _native()
+    from sglang_b200.ops import moe_ops
+
+    g = torch.Generator(device=DEV).manual_seed(H + I)
+    x = torch.randn(T, H, device=DEV, generator=g).to(torch.bfloat16)
+    w13 = (torch.randn(E, 2 * I, H, device=DEV, generator=g) * H ** -0.5).to(torch.bfloat16)
+    w2 = (torch.randn(E, H, I, device=DEV, generator=g) * I ** -0.5).to(torch.bfloat16)
+    ids = torch.stack([torch.randperm(E, device=DEV, generator=g)[:K] for _ in range(T)]).to(torch.int32)
+    w = torch.rand(T, K, device=DEV, generator=g) + 0.1
+    act = ("clamped_glu", 1.5, 1.702)
+    a = moe_ops.fused_moe(x, w13, w2, w, ids, 0, act)
+    fn = lambda gu: ops.clamped_glu(gu.contiguous(), 1.5, 1.702)
+    b = moe_ops._fused_moe_sorted(x, w13, w2, w, ids, 0, fn)
+    ref = torch_ref.fused_moe(x.float(), w13.float(), w2.float(), w, ids, 0, lambda gu: torch_ref.clamped_glu(gu, 1.5, 1.702))
+    scale = ref.abs().max().item()
+    assert (a.float() - ref).abs().max().item() < 0.03 * scale
+    assert (b.float() - ref).abs().max().item() < 0.03 * scale
