@@ -29,15 +29,16 @@ struct LatentParams {
   const int* page_table; int pt_stride; int page_size;
   const int* req_slots; const int* seq_lens; const int* cu_q;
   const float* sinks;
-  int H, R, HG, window;
+  int H, R, RP, HG, window;                    // RP: row stride of the key tile in shared memory (R + 4 when R % 4 == 0, else R + 1)
   float scale;
+  int vec8;
   int nsplit;                                  // decode only: the visible keys of a request are cut into nsplit ranges, one CTA each
   float* part_o; float* part_ml;               // [T, nsplit, H, R] unnormalised outputs and [T, nsplit, H, 2] (running max, sum)
 };
 
 template <typename TCache, int QT, int PP>
 __global__ void __launch_bounds__(NW * 32) latent_attention_kernel(const LatentParams p) {
-  extern __shared__ float sm[];
+  extern __shared__ __align__(16) float sm[];
   const int b = blockIdx.y;
   const int qbase = p.cu_q ? p.cu_q[b] : b;
   const int n = p.cu_q ? p.cu_q[b + 1] - qbase : 1;
@@ -49,9 +50,12 @@ __global__ void __launch_bounds__(NW * 32) latent_attention_kernel(const LatentP
   const int pos0 = L - n + t0;                 // position of the CTA's first query
   const int h0 = blockIdx.z * p.HG;
   const int nh = min(p.HG, p.H - h0);
-  const int R = p.R, RP = R + 1;
+  const int R = p.R, RP = p.RP;
+  const bool vec = (R & 3) == 0;               // 16-byte shared-memory loads of queries and latent rows
+  const bool vec8 = p.vec8 != 0;               // 16-byte global loads of cache rows (rank, row stride and base allow it)
   const int P = nq * nh;                       // (query, head) pairs of this CTA: pair = qi * nh + hi
-  float* s_q = sm;                             // [QT * HG][R]
+  float* s_p = sm;                             // [NW][4][KT] probabilities of the pairs a warp is working on (first: keeps 16-byte alignment)
+  float* s_q = s_p + NW * 4 * KT;              // [QT * HG][R]
   float* s_o = s_q + QT * p.HG * R;            // [QT * HG][R]
   float* s_c = s_o + QT * p.HG * R;            // [KT][R + 1]
   int* s_slot = (int*)(s_c + KT * RP);         // [KT]
@@ -88,10 +92,34 @@ __global__ void __launch_bounds__(NW * 32) latent_attention_kernel(const LatentP
       s_slot[tid] = kp <= last ? pt[kp / p.page_size] * p.page_size + kp % p.page_size : -1;
     }
     __syncthreads();
-    for (int idx = tid; idx < KT * R; idx += NW * 32) {
-      const int k = idx / R, r = idx - k * R;
-      const int slot = s_slot[k];
-      s_c[k * RP + r] = slot >= 0 ? ldc<TCache>(cache + (size_t)slot * p.ldc + r) : 0.f;
+    if (vec8) {                                // 16-byte global loads: 8 bf16 or 2 x 4 fp32 latent values per thread and step
+      const int R8 = R >> 3;
+      for (int idx = tid; idx < KT * R8; idx += NW * 32) {
+        const int k = idx / R8, r = (idx - k * R8) << 3;
+        const int slot = s_slot[k];
+        float v[8];
+        if (slot < 0) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) v[i] = 0.f;
+        } else if (sizeof(TCache) == 2) {
+          const U4 w = ldg128(cache + (size_t)slot * p.ldc + r);
+          v[0] = bf16_lo(w.x); v[1] = bf16_hi(w.x); v[2] = bf16_lo(w.y); v[3] = bf16_hi(w.y);
+          v[4] = bf16_lo(w.z); v[5] = bf16_hi(w.z); v[6] = bf16_lo(w.w); v[7] = bf16_hi(w.w);
+        } else {
+          const float4 w0 = *reinterpret_cast<const float4*>(cache + (size_t)slot * p.ldc + r);
+          const float4 w1 = *reinterpret_cast<const float4*>(cache + (size_t)slot * p.ldc + r + 4);
+          v[0] = w0.x; v[1] = w0.y; v[2] = w0.z; v[3] = w0.w; v[4] = w1.x; v[5] = w1.y; v[6] = w1.z; v[7] = w1.w;
+        }
+        float4* dst = reinterpret_cast<float4*>(s_c + k * RP + r);
+        dst[0] = make_float4(v[0], v[1], v[2], v[3]);
+        dst[1] = make_float4(v[4], v[5], v[6], v[7]);
+      }
+    } else {
+      for (int idx = tid; idx < KT * R; idx += NW * 32) {
+        const int k = idx / R, r = idx - k * R;
+        const int slot = s_slot[k];
+        s_c[k * RP + r] = slot >= 0 ? ldc<TCache>(cache + (size_t)slot * p.ldc + r) : 0.f;
+      }
     }
     __syncthreads();
     const int kp = k0 + lane;
@@ -117,19 +145,23 @@ __global__ void __launch_bounds__(NW * 32) latent_attention_kernel(const LatentP
       float a[PP], a2[PP];
 #pragma unroll
       for (int u = 0; u < PP; ++u) a[u] = a2[u] = 0.f;
-      int r = 0;
-      for (; r + 2 <= R; r += 2) {
-        const float c0 = cv[r], c1 = cv[r + 1];
+      if (vec) {
+        const float4* c4 = reinterpret_cast<const float4*>(cv);
+        for (int r4 = 0; r4 < (R >> 2); ++r4) {
+          const float4 c = c4[r4];
 #pragma unroll
-        for (int u = 0; u < PP; ++u) {
-          a[u] += qv[u][r] * c0;
-          a2[u] += qv[u][r + 1] * c1;
+          for (int u = 0; u < PP; ++u) {
+            const float4 q4 = reinterpret_cast<const float4*>(qv[u])[r4];
+            a[u] += q4.x * c.x + q4.y * c.y;
+            a2[u] += q4.z * c.z + q4.w * c.w;
+          }
         }
-      }
-      if (r < R) {
-        const float c0 = cv[r];
+      } else {
+        for (int r = 0; r < R; ++r) {
+          const float c0 = cv[r];
 #pragma unroll
-        for (int u = 0; u < PP; ++u) a[u] += qv[u][r] * c0;
+          for (int u = 0; u < PP; ++u) a[u] += qv[u][r] * c0;
+        }
       }
       float pj[PP], alpha[PP];
 #pragma unroll
@@ -146,19 +178,32 @@ __global__ void __launch_bounds__(NW * 32) latent_attention_kernel(const LatentP
         l_run[k] = l_run[k] * alpha[u] + warp_sum(pj[u]);
         m_run[k] = m_new;
       }
+      // probabilities go through shared memory: one 16-byte broadcast load brings four keys' weights of a pair
+      float* sp = s_p + warp * 4 * KT;
+#pragma unroll
+      for (int u = 0; u < PP; ++u) sp[u * KT + lane] = pj[u];
+      __syncwarp();
       for (int c0 = 0; c0 < R; c0 += 64) {                  // two column groups per pass
         float acc[PP][2];
 #pragma unroll
         for (int u = 0; u < PP; ++u) acc[u][0] = acc[u][1] = 0.f;
         const int cc0 = min(c0 + lane, R - 1), cc1 = min(c0 + 32 + lane, R - 1);
-#pragma unroll 4
-        for (int j = 0; j < KT; ++j) {
-          const float v0 = s_c[j * RP + cc0], v1 = s_c[j * RP + cc1];
+#pragma unroll 2
+        for (int j = 0; j < KT; j += 4) {
+          float w[PP][4];
 #pragma unroll
           for (int u = 0; u < PP; ++u) {
-            const float pb = __shfl_sync(0xffffffffu, pj[u], j);
-            acc[u][0] += pb * v0;
-            acc[u][1] += pb * v1;
+            const float4 t = *reinterpret_cast<const float4*>(sp + u * KT + j);
+            w[u][0] = t.x; w[u][1] = t.y; w[u][2] = t.z; w[u][3] = t.w;
+          }
+#pragma unroll
+          for (int jj = 0; jj < 4; ++jj) {
+            const float v0 = s_c[(j + jj) * RP + cc0], v1 = s_c[(j + jj) * RP + cc1];
+#pragma unroll
+            for (int u = 0; u < PP; ++u) {
+              acc[u][0] += w[u][jj] * v0;
+              acc[u][1] += w[u][jj] * v1;
+            }
           }
         }
 #pragma unroll
@@ -170,6 +215,7 @@ __global__ void __launch_bounds__(NW * 32) latent_attention_kernel(const LatentP
           if (cb < R) ov[cb] = ov[cb] * alpha[u] + acc[u][1];
         }
       }
+      __syncwarp();                                          // sp is rewritten by the warp's next group of pairs
     }
   }
   __syncwarp();
@@ -226,7 +272,8 @@ void launch_pp(const LatentParams& p, dim3 grid, size_t smem, cudaStream_t strea
 template <typename TCache, int QT>
 void launch(LatentParams p, int B, int max_q_len, int max_kv_len, float* workspace, size_t workspace_floats, cudaStream_t stream) {
   // heads per CTA: as many as fit 200 KB next to the key tile, at most 16 pairs per warp
-  const size_t tile = (size_t)KT * (p.R + 1) * 4 + KT * 4;
+  p.RP = (p.R % 4 == 0) ? p.R + 4 : p.R + 1;
+  const size_t tile = (size_t)KT * p.RP * 4 + KT * 4 + (size_t)NW * 4 * KT * 4;
   const size_t per_head = (size_t)QT * p.R * 4 * 2;
   int hg = (int)std::min<size_t>((size_t)p.H, (200 * 1024 - tile) / per_head);
   hg = std::min(hg, 16 * NW / QT);
@@ -266,7 +313,9 @@ void latent_attention(const float* q, const void* cache, bool cache_bf16, int ld
   if (B > 65535) throw std::runtime_error("sglb latent_attention: more than 65535 requests in one call");
   LatentParams p;
   p.q = q; p.out = out; p.cache = cache; p.ldc = ldc; p.page_table = page_table; p.pt_stride = pt_stride; p.page_size = page_size;
-  p.req_slots = req_slots; p.seq_lens = seq_lens; p.cu_q = cu_q; p.sinks = sinks; p.H = H; p.R = R; p.HG = 1; p.window = window; p.scale = scale; p.nsplit = 1; p.part_o = nullptr; p.part_ml = nullptr;
+  p.req_slots = req_slots; p.seq_lens = seq_lens; p.cu_q = cu_q; p.sinks = sinks; p.H = H; p.R = R; p.RP = R + 1; p.HG = 1;
+  const int esz = cache_bf16 ? 2 : 4;
+  p.vec8 = (R % 8 == 0 && ((size_t)ldc * esz) % 16 == 0 && ((uintptr_t)cache % 16) == 0) ? 1 : 0; p.window = window; p.scale = scale; p.nsplit = 1; p.part_o = nullptr; p.part_ml = nullptr;
   const bool decode = cu_q == nullptr || max_q_len == 1;
   if (cache_bf16) {
     if (decode) launch<__nv_bfloat16, 1>(p, B, 1, max_kv_len, workspace, workspace_floats, stream);
