@@ -149,7 +149,6 @@ def test_latent_attention_reference_op_window_edges_with_a_standout_key():
     later, in a prompt portion and in a decode step, across a page border"""
     R, H, W, ps = 6, 2, 11, 4
     g = torch.Generator().manual_seed(2)
-    Lq = 40
     cache = torch.randn(64 * ps, 1, R + 2, generator=g) * 0.1
     pages = torch.randperm(60, generator=g)[:16] + 1
     pt = torch.zeros(3, 20, dtype=torch.int32)
