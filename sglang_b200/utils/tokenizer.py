@@ -95,7 +95,10 @@ def _content_text(c: Any) -> str:
 
 def get_tokenizer(path: Optional[str], vocab_size: int = 512, eos_token_id: Any = None, bos_token_id: Optional[int] = None,
                   trust_remote_code: bool = False):
-    if path and not path.startswith("dummy:") and os.path.isdir(path):
+    has_files = bool(path) and os.path.isdir(path) and any(
+        os.path.exists(os.path.join(path, f)) for f in ("tokenizer.json", "tokenizer_config.json", "tokenizer.model", "vocab.json", "vocab.txt",
+                                                        "tekken.json", "spiece.model"))
+    if path and not path.startswith("dummy:") and os.path.isdir(path) and has_files:          # a weights-only folder gets the byte tokenizer below
         from transformers import AutoTokenizer
 
         return AutoTokenizer.from_pretrained(path, trust_remote_code=trust_remote_code, local_files_only=True)
