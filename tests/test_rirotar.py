@@ -278,3 +278,14 @@ def test_config_reader_takes_every_size_from_the_file(tmp_path):
     c = load_model_config(str(d))
     assert c.architecture == "Rirotar" and c.hidden_size == 24 and c.vocab_size == 50 and c.num_hidden_layers == 5
     assert c.final_logit_softcapping == 8.0 and c.rms_norm_eps == 1e-5 and c.hybrid["layers"][3]["mixer"]["mask"]["size"] == 19
+
+
+def test_text_prompts_on_a_weights_only_folder(tmp_path):
+    """a folder with only config.json and model.safetensors serves text through the byte tokenizer (what `cli generate` and the HTTP server do)"""
+    h = Harness(tmp_path, _cfg([L(_delta("delta"), _dense()), L(_attn(), None)], vocab=300), seed=8)
+    h.close()
+    eng = sgl.Engine(model_path=os.path.join(str(tmp_path), "m8"), device="cpu", page_size=PAGE, max_total_tokens=256, max_running_requests=2,
+                     log_level="warning")
+    out = eng.generate("hello there", {"max_new_tokens": 4, "temperature": 0.7, "top_k": 5, "ignore_eos": True})
+    assert len(out["output_ids"]) == 4 and isinstance(out["text"], str)
+    eng.shutdown()
