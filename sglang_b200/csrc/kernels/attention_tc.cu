@@ -46,8 +46,6 @@ struct AttnParams {
   int gx, gy, total_items;
   int* sched;         // [0] next item, [1] CTAs finished (the last one resets both: graph-replay safe)
   const unsigned* tree_anc;   // speculative tree verify: [T] bit k of tree_anc[t] = query token t may see draft key `prefix + k` (classic launch)
-  int legacy_epilogue_wait;   // FAULT INJECTION ONLY (SGLB_ATTN_LEGACY_EPILOGUE=1): re-creates the round-1 epilogue hand-off (wait on o_done by
-                              // tile parity) so tools/attn_stress.py can reproduce the premature-pass race / the TP>=4 deadlock it caused
 };
 
 template <int KT, bool HAS_CAP>
@@ -338,8 +336,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     }
 
     // ---- epilogue: wait for the last PV, normalise, store
-    if (p.legacy_epilogue_wait) mbar_wait(o_done, (uint32_t)((n_tiles - 1) & 1));
-    else mbar_wait(o_final, 0);
+    mbar_wait(o_final, 0);
     tc_fence_after();
     if (warp_valid) {
       const float inv_l = (l_i > 0.f) ? 1.f / l_i : 0.f;
@@ -717,8 +714,7 @@ attn_fwd_tc_persist_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
 
       // ---- epilogue: wait for the item's last PV, normalise, store, then hand O back to the MMA warp
       if (lane == 0) SGLB_ATT_DBG(4, n_q, g);
-      if (p.legacy_epilogue_wait) SGLB_ATT_WAIT(o_done, (g - 1) & 1);
-      else SGLB_ATT_WAIT(o_final, n_q & 1);
+      SGLB_ATT_WAIT(o_final, n_q & 1);
       ++n_q;
       tc_fence_after();
       if (warp_valid) {
@@ -838,8 +834,6 @@ void attn_fwd_tc(const void* q, const void* k_cache, const void* v_cache, void* 
   }
   dim3 grid((max_q_len + TQ - 1) / TQ, Hkv * num_splits, B);
   p.gx = (int)grid.x; p.gy = (int)grid.y; p.total_items = (int)(grid.x * grid.y * grid.z); p.sched = sched;
-  static const int legacy = [] { const char* e = getenv("SGLB_ATTN_LEGACY_EPILOGUE"); return (e && e[0] == '1') ? 1 : 0; }();
-  p.legacy_epilogue_wait = legacy;
   // decode (one query token per request) is latency-bound: small KV tiles, two CTAs per SM
   const bool small = (cu_q == nullptr) && page_size <= 64;
   const bool capped = logit_cap > 0.f;
