@@ -56,7 +56,7 @@ def _paged(seq_lens, page_size, width, dtype, seed):
 
 
 @pytest.mark.parametrize("cdt", [torch.bfloat16, torch.float32])
-@pytest.mark.parametrize("R,H,window", [(40, 5, 19), (64, 6, 136), (128, 3, -1), (24, 17, 1)])
+@pytest.mark.parametrize("R,H,window", [(40, 5, 19), (72, 7, 141), (128, 3, -1), (24, 17, 1)])
 def test_latent_attention_prefill_and_decode(cdt, R, H, window):
     _native()
     ps = 16
@@ -248,6 +248,58 @@ def test_engine_on_cuda_with_sizes_no_vector_lane_divides(tmp_path, dtype, tol):
         err = lambda x, y: float(np.quantile(np.sqrt(((x - y) ** 2).mean(-1)), 0.5))
     assert err(h.step([("w", a, range(len(a)))], ["w"]), ra) < tol
     assert err(h.run_cut("c", a, [3, 40, 2, 17]), ra) < tol
+    h.close()
+
+
+@pytest.mark.parametrize("seed", [0, 1, 2, 3])
+def test_engine_on_cuda_with_randomly_drawn_stacks(tmp_path, seed):
+    """layer order, head counts, head sizes, ranks, windows, taps, expert counts and groups drawn at random (fp32, so the oracle is a strict
+    reference): a whole prompt, portions, and three requests batched with one of them decoding beside the others' portions"""
+    import numpy as np
+
+    from test_rirotar import L, Harness, _attn, _cfg, _delta, _dense, _moe, _tokens
+
+    rng = np.random.default_rng(500 + seed)
+    ch = lambda xs: xs[int(rng.integers(0, len(xs)))]
+    layers = []
+    for _ in range(int(rng.integers(2, 6))):
+        kind = ch(["delta", "channel_delta", "latent_attention"])
+        if kind == "latent_attention":
+            mix = _attn(heads=ch([1, 2, 3, 5, 8, 12]), dim=ch([16, 24, 48, 64, 128]), vdim=ch([16, 40, 64, 96, 128]), kv_rank=ch([16, 24, 48, 96, 192]),
+                        window=ch([1, 2, 17, 64, 100, 200, 1000]), scale=ch([0.125, 0.25, 0.09]))
+        else:
+            kvh = ch([1, 2, 3, 4])
+            mix = _delta(kind, heads=kvh * ch([1, 2, 3]), kv_heads=kvh, dim=ch([16, 48, 64, 128]), vdim=ch([16, 48, 64, 128]), conv=ch([2, 4, 5]),
+                         **({"rank": ch([4, 8, 16])} if kind == "channel_delta" else {}))
+        m = ch(["dense", "moe", "moe", None])
+        if m == "moe":
+            cnt, per = ch([1, 2, 4]), ch([1, 2, 3, 4])
+            keep = int(rng.integers(1, cnt + 1))
+            mlp = _moe(experts=cnt * per, top=int(rng.integers(1, min(keep * per, 6) + 1)), count=cnt, keep=keep, ff=ch([32, 48, 40, 128]),
+                       limit=ch([1.0, 3.0]), scale=ch([1.0, 2.5]))
+        else:
+            mlp = _dense(ff=ch([96, 200]), limit=ch([1.0, 7.0])) if m else None
+        layers.append(L(mix, mlp))
+    V = ch([160, 300, 512])
+    cfg = _cfg(layers, width=ch([48, 96, 160, 256]), vocab=V, softcap=ch([0.0, 15.0]), eps=ch([1e-5, 1e-6]))
+    h = Harness(tmp_path, cfg, seed=seed, device="cuda", dtype="float32", page=64, max_tokens=1024)
+    a, b, c = _tokens(230, V, seed), _tokens(70, V, seed + 50), _tokens(110, V, seed + 99)
+    ra, rb, rc = h.oracle(a), h.oracle(b), h.oracle(c)
+    err = lambda x, y: float(np.abs(x - y).max())
+    assert err(h.step([("w", a, range(len(a)))], ["w"]), ra) < 5e-4
+    assert err(h.run_cut("c", a[:200], [2, 61, 3, 64, 37, 5]), ra[:200]) < 5e-4
+    got = {"a": [], "b": [], "c": [h.step([("c", c[:100], range(100))])]}
+    pa = pb = 0
+    for i, (sa, sb) in enumerate(zip([50, 2, 77, 1, 1, 64, 35], [0, 33, 2, 35, 0, 0, 0])):
+        ent = [(r, t[p:p + n], range(n)) for r, t, p, n in (("a", a, pa, sa), ("b", b, pb, sb)) if n] + [("c", c[100 + i:101 + i], range(1))]
+        out = h.step(ent, [r for r, t, p, n in (("a", a, pa, sa), ("b", b, pb, sb)) if n and p + n == len(t)])
+        at = 0
+        for r, toks, _ in ent:
+            got[r].append(out[at:at + len(toks)])
+            at += len(toks)
+        pa, pb = pa + sa, pb + sb
+    h.step([("c", c[107:108], [0])], ["c"])
+    assert err(np.concatenate(got["a"]), ra) < 5e-4 and err(np.concatenate(got["b"]), rb) < 5e-4 and err(np.concatenate(got["c"]), rc[:107]) < 5e-4
     h.close()
 
 
