@@ -377,6 +377,31 @@ def rirotar_config(hf: Dict[str, Any]) -> Dict[str, Any]:
                 hybrid={"layers": layers})
 
 
+def zaparax_config(hf: Dict[str, Any]) -> Dict[str, Any]:
+    """Zaparax ``config.json`` -> ModelConfig fields.  ``layers[i]`` = ``type`` of the mixer (``mamba2`` | ``attention``), its sizes under
+    ``mixer``, the feed-forward under ``mlp`` or null; ``loop`` = ``{start, stop, times}`` (layers ``start .. stop - 1`` run ``times`` times with
+    the same weights); ``embedding`` = ``{scale, bigram: {buckets, mul_prev, mul_cur}}``; globals ``width``, ``vocab``, ``norm.eps``.  The flat
+    fields are summaries for code that sizes buffers; the model reads ``hybrid``."""
+    layers = [dict(l) for l in hf["layers"]]
+    width = int(hf["width"])
+    moes = [l["mlp"] for l in layers if l.get("mlp")]
+    ffs = [int(m["expert"]["ff"]) * int(m["router"]["top"]) + int((m.get("shared") or {}).get("ff", 0)) for m in moes]
+    attn = [l["mixer"] for l in layers if l["type"] == "attention"]
+    heads = max([int(l["mixer"]["heads"]) for l in layers] or [1])
+    return dict(architecture="Zaparax", hidden_size=width, vocab_size=int(hf["vocab"]), num_hidden_layers=len(layers),
+                rms_norm_eps=float((hf.get("norm") or {}).get("eps", 1e-6)), final_logit_softcapping=0.0,
+                num_attention_heads=heads, num_key_value_heads=1, head_dim=max([int(m["dim"]) for m in attn] or [width // heads]),
+                intermediate_size=max(ffs or [width]), num_local_experts=max([int(m["router"]["experts"]) for m in moes] or [0]),
+                num_experts_per_tok=max([int(m["router"]["top"]) for m in moes] or [0]),
+                max_position_embeddings=int(hf.get("max_positions") or (1 << 20)), tie_word_embeddings=False, eos_token_id=None,
+                dtype={"float16": "float16", "float32": "float32"}.get(hf.get("dtype") or "bfloat16", "bfloat16"),
+                hybrid={"layers": layers, "loop": hf.get("loop") or None, "embedding": hf.get("embedding") or {}})
+
+
+# configurations that list their layers one by one, chosen by the file's ``architecture`` key
+_LAYER_LIST_READERS = {"Rirotar": rirotar_config, "Zaparax": zaparax_config}
+
+
 def _has_native_class(arch: str) -> bool:
     from ..models.registry import supported_architectures
 
@@ -422,8 +447,8 @@ def load_model_config(model_path: str, overrides: Optional[Dict[str, Any]] = Non
                 raise FileNotFoundError(f"{cfg_file} not found (offline box: use dummy:<preset>, a local HF directory or a .gguf file)")
             with open(cfg_file) as f:
                 hf = json.load(f)
-        if hf.get("architecture") == "Rirotar":
-            kw = rirotar_config(hf)
+        if hf.get("architecture") in _LAYER_LIST_READERS:
+            kw = _LAYER_LIST_READERS[hf["architecture"]](hf)
             kw["name"] = os.path.basename(model_path.rstrip("/"))
             kw.update(overrides)
             cfg = ModelConfig(**kw)

@@ -51,6 +51,16 @@ def grouped_sigmoid_route(logits: torch.Tensor, top_k: int, n_groups: int = 1, k
     return w.contiguous(), ids.to(torch.int32).contiguous()
 
 
+def softmax_bias_route(logits: torch.Tensor, correction, top_k: int, n_real: int):
+    """Soft-max router whose last columns are identity experts, fp32: scores ``s = softmax(logits)`` over every column; the ``top_k`` largest
+    ``s + correction`` are chosen (the correction steers the choice only) and weighted by their plain ``s``, not renormalised.  Columns
+    ``>= n_real`` have no weights: such an expert returns its input, so their chosen scores are summed into one number per token.
+    -> (weights fp32 [T, top_k] (0 where an identity expert was chosen), expert ids int32 [T, top_k], identity weight fp32 [T])"""
+    from ..ops import moe_ops
+
+    return moe_ops.softmax_bias_route(logits, correction, top_k, n_real)
+
+
 class FusedMoE(nn.Module):
     def __init__(self, num_experts: int, top_k: int, hidden_size: int, intermediate_size: int, dtype=torch.bfloat16,
                  renormalize: bool = True, ep_size: int = 1, quant=None, layer_id: int = 0):

@@ -1,0 +1,88 @@
+"""Grouped-query attention without positional rotation whose scores carry the position instead:
+
+    q, k      each head divided by its root mean square (no weight);  q_i also times  1 + coef * ln(floor((i + 1) / every) + 1)
+    s_ij      = cap * tanh(q_i . k_j * scale / cap)  -  slope_h * (i - j)            slope_h = 2^(-8 (h + 1) / H)
+    visible   0 <= i - j < window
+    p_ij      = exp(s_ij) / (exp(sink_h) + sum_j' exp(s_ij'))                          the sink has no key and no value
+
+The projections are one GEMM with their biases in the epilogue; ``ops.qk_norm_cache_write`` normalises q and k, applies the query
+temperature and writes k / v rows into the paged pool; ``ops.window_attention`` (csrc/kernels/window_attention.cu) is the attention itself,
+one kernel for prompt portions and decode tokens.  Cap, bias, mask, sink and soft-max are fp32; the cache is in the model dtype.
+
+The paged pool holds one flat row per token and plane (``cache_width`` columns, the widest layer's ``kv_heads * max(dim, vdim)``): a layer
+reads the first ``kv_heads * dim`` columns of the key plane as its key heads, so layers of different head counts and sizes share one pool.
+``cache_idx`` selects the pool layer: a layer that runs several times per forward owns one pool layer per run.  The window only masks — pages
+behind the window stay with the request until it ends.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+from torch import nn
+
+from .. import ops
+from ..model_executor.forward_batch import ForwardBatch
+
+
+class FlatCacheSpec:
+    """what the model runner reads to size the paged pool: one "KV head" of ``cache_width`` per token in a key and a value plane"""
+
+    def __init__(self, num_heads: int, cache_width: int, layer_id: int, scale: float, window: int):
+        self.num_heads, self.num_kv_heads, self.head_dim, self.kv_head_dim = num_heads, 1, cache_width, cache_width
+        self.latent_v_dim = 0
+        self.layer_id, self.scale, self.window, self.logit_cap, self.rope, self.sinks = layer_id, scale, window, 0.0, None, None
+
+
+def distance_slopes(heads: int, base: float = 8.0) -> torch.Tensor:
+    """slope_h = 2^(-base (h + 1) / heads), h = 0 .. heads - 1"""
+    return torch.pow(2.0, -base * torch.arange(1, heads + 1, dtype=torch.float64) / heads).float()
+
+
+class BiasedWindowAttention(nn.Module):
+    def __init__(self, width: int, heads: int, kv_heads: int, dim: int, vdim: int, scale: Optional[float], softcap: float, window: int, eps: float,
+                 dtype, temp_coef: float = 0.0, temp_every: int = 1, qk_norm: bool = True, distance_bias: bool = True, sinks: bool = True,
+                 bias: bool = True):
+        super().__init__()
+        assert heads % kv_heads == 0
+        self.H, self.G, self.D, self.Dv = heads, kv_heads, dim, vdim
+        self.eps, self.softcap, self.window = eps, float(softcap or 0.0), int(window or -1)
+        self.scale = float(scale) if scale is not None else dim ** -0.5
+        self.temp_coef, self.temp_every, self.qk_norm = float(temp_coef), int(temp_every), qk_norm
+        n = heads * dim + kv_heads * dim + kv_heads * vdim
+        self.qkv_weight = nn.Parameter(torch.zeros(n, width, dtype=dtype), requires_grad=False)          # rows [q | k | v]: one GEMM
+        self.qkv_bias = nn.Parameter(torch.zeros(n, dtype=dtype), requires_grad=False) if bias else None
+        self.o_weight = nn.Parameter(torch.zeros(width, heads * vdim, dtype=dtype), requires_grad=False)
+        self.sinks = nn.Parameter(torch.zeros(heads, dtype=torch.float32), requires_grad=False) if sinks else None
+        self.slopes = nn.Parameter(distance_slopes(heads), requires_grad=False) if distance_bias else None
+
+    @property
+    def cache_width(self) -> int:
+        return self.G * max(self.D, self.Dv)
+
+    def load(self, leaf: str, w: torch.Tensor) -> bool:
+        hd, gd = self.H * self.D, self.G * self.D
+        rows = {"q": (0, hd), "k": (hd, hd + gd), "v": (hd + gd, hd + gd + self.G * self.Dv)}
+        if leaf in rows:
+            a, b = rows[leaf]
+            self.qkv_weight.data[a:b].copy_(w)
+        elif leaf.endswith(".b") and leaf[:-2] in rows and self.qkv_bias is not None:
+            a, b = rows[leaf[:-2]]
+            self.qkv_bias.data[a:b].copy_(w)
+        elif leaf == "sink" and self.sinks is not None:
+            self.sinks.data.copy_(w.float())
+        elif leaf == "o":
+            self.o_weight.data.copy_(w)
+        else:
+            return False
+        return True
+
+    def forward(self, h: torch.Tensor, fb: ForwardBatch, cache_idx: int) -> torch.Tensor:
+        T = h.shape[0]
+        qkv = ops.linear(h, self.qkv_weight, self.qkv_bias)
+        kc, vc = fb.kv_pool.k(cache_idx), fb.kv_pool.v(cache_idx)                  # [slots, 1, cache_width] each
+        q = ops.qk_norm_cache_write(qkv, self.H, self.G, self.D, self.Dv, fb.positions, self.eps, self.temp_coef, self.temp_every, kc, vc,
+                                    fb.out_cache_loc, self.qk_norm)
+        o = ops.window_attention(q, kc, vc, self.G, self.Dv, fb.page_table, fb.req_slots, fb.seq_lens, fb.cu_q, fb.q_lens, fb.max_q_len, fb.page_size,
+                                 self.scale, self.softcap, self.window, self.slopes, self.sinks)
+        return ops.linear(o.view(T, self.H * self.Dv), self.o_weight)

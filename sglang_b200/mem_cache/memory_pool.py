@@ -192,15 +192,20 @@ class LayeredStatePool:
     written against one works against the other.  A slot needs no clearing on reuse: the kernels start a request whose cached length is
     zero from a zero state and zero convolution history."""
 
-    def __init__(self, slots: int, geometry, dtype: torch.dtype, device):
-        """geometry: one ``(conv_channels, taps, heads, key_dim, value_dim)`` per recurrent layer"""
+    def __init__(self, slots: int, geometry, dtype: torch.dtype, device, token_history: bool = False):
+        """geometry: one ``(conv_channels, taps, heads, key_dim, value_dim)`` per recurrent layer.  ``token_history``: also keep every
+        request's last token id (``tokens`` int32 [slots]) for embeddings that look one token back (``ops.bigram_embedding``)."""
         self.slots = slots
         self.conv = [torch.zeros(slots, c, max(1, k - 1), dtype=dtype, device=device) for c, k, _, _, _ in geometry]
         self.ssm = [torch.zeros(slots, h, dk, dv, dtype=torch.float32, device=device) for _, _, h, dk, dv in geometry]
+        self.tokens = torch.zeros(slots, dtype=torch.int32, device=device) if token_history else None
+
+    def _all(self):
+        return self.conv + self.ssm + ([self.tokens] if self.tokens is not None else [])
 
     def bytes(self) -> int:
-        return sum(t.numel() * t.element_size() for t in self.conv + self.ssm)
+        return sum(t.numel() * t.element_size() for t in self._all())
 
     def copy_row(self, src: int, dst: int) -> None:
-        for t in self.conv + self.ssm:
+        for t in self._all():
             t[dst].copy_(t[src])

@@ -145,6 +145,9 @@ def _register_builtins() -> None:
     from . import rirotar as _rr
 
     register_model("Rirotar", _rr.RirotarForCausalLM)
+    from . import zaparax as _zp
+
+    register_model("Zaparax", _zp.ZaparaxForCausalLM)
     from . import transformers_fallback as _tff
 
     register_model("TransformersForCausalLM", _tff.TransformersForCausalLM)

@@ -438,9 +438,18 @@ def merge_attn_states(o1, lse1, o2, lse2):
 
 # ------------------------------------------------------------------ fp32 residual stream / latent attention / gated delta rule / clamped GLU
 def add_rmsnorm_f32(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float, zero_centred: bool = False,
-                    out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+                    out_dtype: torch.dtype = torch.bfloat16, post_weight: Optional[torch.Tensor] = None) -> torch.Tensor:
     """fp32 residual stream: ``residual += delta`` (in place, fp32 sum) and the RMS norm of the new residual in ``out_dtype``, one kernel
-    (csrc/kernels/residual_f32.cu).  ``zero_centred``: the weight is stored around zero and applied as ``1 + w``."""
+    (csrc/kernels/residual_f32.cu).  ``zero_centred``: the weight is stored around zero and applied as ``1 + w``.  ``post_weight``: the branch
+    output is itself RMS-normed, times ``1 + post_weight``, before it joins the residual (sandwich-norm blocks), in the same kernel."""
+    if post_weight is not None and delta is not None:
+        assert zero_centred
+        if _use_native(residual) and residual.dtype == torch.float32 and residual.is_contiguous() and out_dtype in (torch.bfloat16, torch.float32) \
+                and delta.dtype in (torch.bfloat16, torch.float32) and delta.is_contiguous() and weight.dtype == out_dtype and post_weight.dtype == out_dtype:
+            out = torch.empty(residual.shape, dtype=out_dtype, device=residual.device)
+            torch.ops.sglb.postnorm_add_rmsnorm_f32(residual, delta, post_weight, weight, out, float(eps))
+            return out
+        return torch_ref.postnorm_add_rmsnorm_f32(residual, delta, post_weight, weight, eps, out_dtype)
     if _use_native(residual) and residual.dtype == torch.float32 and residual.is_contiguous() and out_dtype in (torch.bfloat16, torch.float32) \
             and (delta is None or (delta.dtype in (torch.bfloat16, torch.float32) and delta.is_contiguous())):
         out = torch.empty(residual.shape, dtype=out_dtype, device=residual.device)
@@ -504,3 +513,73 @@ def gated_delta_rule(u: torch.Tensor, Hk: int, Dk: int, H: int, Dv: int, a_raw: 
         return out
     return torch_ref.gated_delta_rule(u, Hk, Dk, H, Dv, a_raw, A_log, dt_bias, b_raw, state, req_slots, seq_lens, q_lens, gate_raw, norm_w, eps,
                                       gate_act, per_channel)
+
+
+# ------------------------------------------------------------------ bigram embedding / Mamba-2 scan / biased window attention / soft-max router with identity experts
+def bigram_embedding(embed: torch.Tensor, bigram: Optional[torch.Tensor], ids: torch.Tensor, prev_tokens: Optional[torch.Tensor], cu_q,
+                     req_slots: torch.Tensor, seq_lens: torch.Tensor, max_q_len: int, scale: float, mul_prev: int = 0, mul_cur: int = 0,
+                     buckets: int = 0) -> torch.Tensor:
+    """token embedding times ``scale`` plus a hashed (previous token, token) row, straight into the fp32 residual stream
+    (csrc/kernels/elementwise.cu; contract in ``torch_ref.bigram_embedding``).  ``prev_tokens`` int32 [slots] carries every request's last
+    token from call to call."""
+    if _use_native(embed) and embed.dtype in (torch.bfloat16, torch.float32) and embed.is_contiguous() and ids.dtype == torch.int32 \
+            and req_slots.numel() <= 65535 and (bigram is None or (bigram.dtype == embed.dtype and bigram.is_contiguous())):
+        out = torch.empty(ids.shape[0], embed.shape[1], dtype=torch.float32, device=embed.device)
+        torch.ops.sglb.bigram_embedding(embed, bigram, ids.contiguous(), prev_tokens if bigram is not None else None, cu_q, req_slots, seq_lens,
+                                        int(max_q_len), float(scale), int(mul_prev), int(mul_cur), int(buckets), out)
+        return out
+    return torch_ref.bigram_embedding(embed, bigram, ids, prev_tokens, cu_q, req_slots, seq_lens, scale, mul_prev, mul_cur, buckets)
+
+
+def grouped_rmsnorm(x: torch.Tensor, weight: torch.Tensor, groups: int, eps: float, out_dtype: torch.dtype) -> torch.Tensor:
+    """fp32 [T, C] in ``groups`` equal parts, each divided by its own root mean square, times weight (csrc/kernels/residual_f32.cu)"""
+    if _use_native(x) and x.dtype == torch.float32 and x.is_contiguous() and out_dtype in (torch.bfloat16, torch.float32) and weight.dtype == out_dtype \
+            and x.shape[1] % groups == 0:
+        out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+        torch.ops.sglb.grouped_rmsnorm(x, weight, int(groups), float(eps), out)
+        return out
+    return torch_ref.grouped_rmsnorm(x, weight, groups, eps, out_dtype)
+
+
+def mamba2_scan(u: torch.Tensor, z: Optional[torch.Tensor], dt_raw: torch.Tensor, dt_bias: torch.Tensor, A_log: torch.Tensor, D: Optional[torch.Tensor],
+                state: torch.Tensor, req_slots: torch.Tensor, seq_lens: torch.Tensor, cu_q: Optional[torch.Tensor], q_lens: Optional[torch.Tensor],
+                H: int, P: int, N: int, G: int) -> torch.Tensor:
+    """Mamba-2 recurrence over a ragged batch (prompt portions and single decode tokens alike): softplus step size, decay, the fp32 state update
+    and read-out, the skip term and the silu(z) gate in one kernel (csrc/kernels/mamba.cu; contract in ``torch_ref.mamba2_scan``).  ``z`` and
+    ``dt_raw`` may be column views of the projection's output."""
+    if (_use_native(u) and u.dtype == torch.float32 and u.is_contiguous() and state.dtype == torch.float32 and N <= 1024 and req_slots.numel() <= 65535
+            and dt_raw.stride(1) == 1 and dt_raw.dtype in (torch.bfloat16, torch.float32) and (z is None or (z.stride(1) == 1 and z.dtype == dt_raw.dtype))):
+        out = torch.empty(u.shape[0], H * P, dtype=torch.float32, device=u.device)
+        f = lambda t: None if t is None else t.float().contiguous()
+        torch.ops.sglb.mamba2_scan(u, z, dt_raw, f(dt_bias), f(A_log), f(D), state, req_slots, seq_lens, cu_q, int(H), int(P), int(N), int(G), out)
+        return out
+    return torch_ref.mamba2_scan(u, z, dt_raw, dt_bias, A_log, D, state, req_slots, seq_lens, q_lens, H, P, N, G)
+
+
+def qk_norm_cache_write(qkv: torch.Tensor, H: int, G: int, D: int, Dv: int, positions: torch.Tensor, eps: float, temp_coef: float, temp_every: int,
+                        k_cache: torch.Tensor, v_cache: torch.Tensor, out_cache_loc: torch.Tensor, normalise: bool = True) -> torch.Tensor:
+    """per-head unit-RMS q and k, position-dependent query temperature, and the write of k / v rows into the paged cache, one kernel
+    (csrc/kernels/window_attention.cu; contract in ``torch_ref.qk_norm_cache_write``).  Returns q [T, H, D] in the cache dtype."""
+    if (_use_native(qkv) and qkv.dtype in (torch.bfloat16, torch.float32) and qkv.is_contiguous() and k_cache.dtype == qkv.dtype and v_cache.dtype == qkv.dtype
+            and k_cache.stride(-1) == 1 and v_cache.stride(-1) == 1 and k_cache.stride(0) == v_cache.stride(0)):
+        q = torch.empty(qkv.shape[0], H, D, dtype=qkv.dtype, device=qkv.device)
+        torch.ops.sglb.qk_norm_cache_write(qkv, int(H), int(G), int(D), int(Dv), positions, float(eps), float(temp_coef), int(max(1, temp_every)), k_cache,
+                                           v_cache, out_cache_loc, bool(normalise), q)
+        return q
+    return torch_ref.qk_norm_cache_write(qkv, H, G, D, Dv, positions, eps, temp_coef, max(1, temp_every), k_cache, v_cache, out_cache_loc, normalise)
+
+
+def window_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, G: int, Dv: int, page_table: torch.Tensor, req_slots: torch.Tensor,
+                     seq_lens: torch.Tensor, cu_q: Optional[torch.Tensor], q_lens: Optional[torch.Tensor], max_q_len: int, page_size: int, scale: float,
+                     softcap: float = 0.0, window: int = -1, slopes: Optional[torch.Tensor] = None, sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """paged grouped-query attention with a tanh score cap, a per-head distance bias, a sliding window and soft-max sinks, for prompt portions
+    and decode tokens (csrc/kernels/window_attention.cu; contract in ``torch_ref.window_attention``).  Returns [T, H, Dv] in q's dtype."""
+    T, H, D = q.shape
+    if (_use_native(q) and q.dtype in (torch.bfloat16, torch.float32) and q.is_contiguous() and k_cache.dtype == q.dtype and v_cache.dtype == q.dtype
+            and D <= 256 and Dv <= 256 and req_slots.numel() <= 65535 and k_cache.stride(0) == v_cache.stride(0)):
+        out = torch.empty(T, H, Dv, dtype=q.dtype, device=q.device)
+        torch.ops.sglb.window_attention(q, k_cache, v_cache, int(G), int(Dv), page_table, req_slots, seq_lens, cu_q, int(max_q_len), int(page_size),
+                                        float(scale), float(softcap), int(window), slopes, sinks, out)
+        return out
+    return torch_ref.window_attention(q, k_cache, v_cache, G, Dv, page_table, req_slots, seq_lens, q_lens, page_size, scale, softcap, window, slopes,
+                                      sinks).to(q.dtype)

@@ -78,3 +78,31 @@ def _fused_moe_sorted(x, w13, w2, topk_w, topk_ids, expert_offset, act=None):
         out.index_add_(0, tok[off:off + c], y)
         off += c
     return out.to(x.dtype)
+
+
+def softmax_bias_route(logits: torch.Tensor, correction, top_k: int, n_real: int):
+    """soft-max scores over real and identity experts, choice by ``score + correction``, weights = the chosen plain scores (warp-per-token
+    kernel in csrc/kernels/moe.cu; contract in ``torch_ref.softmax_bias_route``) -> (weights, ids, summed weight of the identity picks)"""
+    T, E = logits.shape
+    if logits.is_cuda and _has("moe_softmax_bias_route") and logits.dtype == torch.float32 and logits.stride(1) == 1 and E <= 1024 and top_k <= 32:
+        w = torch.empty(T, top_k, dtype=torch.float32, device=logits.device)
+        ids = torch.empty(T, top_k, dtype=torch.int32, device=logits.device)
+        ident = torch.empty(T, dtype=torch.float32, device=logits.device)
+        torch.ops.sglb.moe_softmax_bias_route(logits, None if correction is None else correction.float().contiguous(), int(n_real), w, ids, ident)
+        return w, ids, ident
+    return torch_ref.softmax_bias_route(logits, correction, top_k, n_real)
+
+
+def moe_combine(y: torch.Tensor, h: torch.Tensor, ident_w, shared, shared_logit) -> torch.Tensor:
+    """y + ident_w * h + sigmoid(shared_logit) * shared, rows of [T, width] (identity experts return their input; the always-on expert is gated
+    by one number per token); fp32 sums (csrc/kernels/moe.cu)"""
+    if y.is_cuda and _has("moe_combine") and y.dtype in (torch.bfloat16, torch.float32) and y.is_contiguous() and h.is_contiguous() and h.dtype == y.dtype \
+            and (shared is None or (shared.is_contiguous() and shared.dtype == y.dtype and shared_logit is not None and shared_logit.stride(0) >= 1)):
+        torch.ops.sglb.moe_combine(y, h, ident_w, shared, None if shared is None else shared_logit.float().contiguous())
+        return y
+    out = y.float()
+    if ident_w is not None:
+        out = out + ident_w.float()[:, None] * h.float()
+    if shared is not None:
+        out = out + torch.sigmoid(shared_logit.float()).reshape(-1, 1) * shared.float()
+    return out.to(y.dtype)

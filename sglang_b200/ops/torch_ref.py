@@ -476,3 +476,161 @@ def gated_delta_rule(u: torch.Tensor, Hk: int, Dk: int, H: int, Dv: int, a_raw: 
         z = gate_raw.float().view(T, H, Dv)
         out = out * (F.silu(z) if gate_act == "silu" else torch.sigmoid(z))
     return out
+
+
+# ------------------------------------------------------------------ Zaparax mechanisms: bigram embedding, post-normed residual, Mamba-2 scan, biased window attention
+def bigram_embedding(embed: torch.Tensor, bigram: Optional[torch.Tensor], ids: torch.Tensor, prev_tokens: Optional[torch.Tensor], cu_q,
+                     req_slots: torch.Tensor, seq_lens: torch.Tensor, scale: float, mul_prev: int, mul_cur: int, buckets: int) -> torch.Tensor:
+    """fp32 [T, width] = embed[id] * scale + bigram[(prev * mul_prev + id * mul_cur) mod buckets]; a sequence's first token takes row
+    ``buckets``.  ``prev_tokens`` int32 [slots] holds every request's last token between calls (updated in place); ``cu_q`` None = one token per
+    request."""
+    x = embed[ids.long()].float() * scale
+    if bigram is None:
+        return x
+    B = req_slots.numel()
+    cu = cu_q.tolist() if cu_q is not None else list(range(B + 1))
+    idl = ids.long()
+    prev = torch.roll(idl, 1)
+    first = torch.zeros_like(idl, dtype=torch.bool)
+    for b in range(B):
+        q0, n = cu[b], cu[b + 1] - cu[b]
+        if n <= 0:
+            continue
+        s = int(req_slots[b])
+        if int(seq_lens[b]) - n == 0:
+            first[q0] = True
+        else:
+            prev[q0] = prev_tokens[s].long()
+        prev_tokens[s] = idl[q0 + n - 1].to(prev_tokens.dtype)
+    row = (prev * mul_prev + idl * mul_cur) % buckets
+    row = torch.where(first, torch.full_like(row, buckets), row)
+    return x + bigram[row].float()
+
+
+def postnorm_add_rmsnorm_f32(residual: torch.Tensor, delta: Optional[torch.Tensor], post_weight: torch.Tensor, weight: torch.Tensor, eps: float,
+                             out_dtype: torch.dtype) -> torch.Tensor:
+    """residual (fp32, in place) += rmsnorm(delta) * (1 + post_weight); returns rmsnorm(residual) * (1 + weight) in ``out_dtype``"""
+    d = delta.float()
+    residual.add_(d * torch.rsqrt(d.pow(2).mean(-1, keepdim=True) + eps) * (1.0 + post_weight.float()))
+    y = residual * torch.rsqrt(residual.pow(2).mean(-1, keepdim=True) + eps)
+    return (y * (1.0 + weight.float())).to(out_dtype)
+
+
+def grouped_rmsnorm(x: torch.Tensor, weight: torch.Tensor, groups: int, eps: float, out_dtype: torch.dtype) -> torch.Tensor:
+    """x [T, C] cut into ``groups`` equal parts, each divided by its own root mean square, times weight [C]"""
+    T, C = x.shape
+    xf = x.float().view(T, groups, C // groups)
+    y = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
+    return (y.view(T, C) * weight.float()).to(out_dtype)
+
+
+def mamba2_scan(u: torch.Tensor, z: Optional[torch.Tensor], dt_raw: torch.Tensor, dt_bias: torch.Tensor, A_log: torch.Tensor, D: Optional[torch.Tensor],
+                state: torch.Tensor, req_slots: torch.Tensor, seq_lens: torch.Tensor, q_lens: Optional[torch.Tensor], H: int, P: int, N: int,
+                G: int) -> torch.Tensor:
+    """Mamba-2 recurrence over a ragged batch, token by token, state in place.
+
+    u fp32 [T, H*P + 2*G*N] = short-conv outputs [x | B | C]; head h reads B / C group ``h // (H // G)``.  dt = softplus(dt_raw + dt_bias) [T, H]
+    (no clamp).  state fp32 [slots, H, N, P]; a request whose ``seq_len == q_len`` starts from zero.  Per token and head:
+    S <- exp(-exp(A_log) dt) S + dt B x^T;  y = S^T C + D x;  with ``z``: y <- y * silu(z).  Returns fp32 [T, H*P]."""
+    T = u.shape[0]
+    inner = H * P
+    rep = H // G
+    x = u[:, :inner].float().view(T, H, P)
+    Bm = u[:, inner:inner + G * N].float().view(T, G, N).repeat_interleave(rep, 1)
+    Cm = u[:, inner + G * N:inner + 2 * G * N].float().view(T, G, N).repeat_interleave(rep, 1)
+    dt = F.softplus(dt_raw.float() + dt_bias.float(), threshold=1e9)
+    dA = torch.exp(-A_log.float().exp()[None, :] * dt)
+    out = torch.empty(T, H, P, dtype=torch.float32, device=u.device)
+    off = 0
+    for b in range(req_slots.shape[0]):
+        n = 1 if q_lens is None else int(q_lens[b])
+        if n <= 0:
+            continue
+        slot = int(req_slots[b])
+        S = torch.zeros_like(state[slot]) if int(seq_lens[b]) - n == 0 else state[slot].clone()
+        for t in range(off, off + n):
+            S = S * dA[t][:, None, None] + (dt[t][:, None] * Bm[t])[:, :, None] * x[t][:, None, :]
+            out[t] = torch.einsum("hnp,hn->hp", S, Cm[t])
+        state[slot] = S
+        off += n
+    if D is not None:
+        out = out + D.float()[None, :, None] * x
+    out = out.reshape(T, inner)
+    if z is not None:
+        out = out * F.silu(z.float())
+    return out
+
+
+def qk_norm_cache_write(qkv: torch.Tensor, H: int, G: int, D: int, Dv: int, positions: torch.Tensor, eps: float, temp_coef: float, temp_every: int,
+                        k_cache: torch.Tensor, v_cache: torch.Tensor, out_cache_loc: torch.Tensor, normalise: bool = True) -> torch.Tensor:
+    """qkv [T, H*D + G*D + G*Dv] -> q [T, H, D] (cache dtype) with every head divided by its root mean square and multiplied by the
+    position's query temperature ``1 + coef * ln(floor((p + 1) / every) + 1)``; the heads of k (same unit-RMS form) go to the first
+    ``G*D`` columns of ``k_cache[loc]`` and v to the first ``G*Dv`` columns of ``v_cache[loc]`` (caches [slots, 1, width])."""
+    T = qkv.shape[0]
+    q = qkv[:, :H * D].float().view(T, H, D)
+    k = qkv[:, H * D:H * D + G * D].float().view(T, G, D)
+    v = qkv[:, H * D + G * D:].float()
+    if normalise:
+        q = q * torch.rsqrt(q.pow(2).mean(-1, keepdim=True) + eps)
+        k = k * torch.rsqrt(k.pow(2).mean(-1, keepdim=True) + eps)
+    if temp_coef != 0.0:
+        p1 = positions.long() + 1
+        q = q * (1.0 + temp_coef * torch.log((p1 // int(temp_every)).float() + 1.0))[:, None, None]
+    loc = out_cache_loc.long()
+    k_cache[loc, 0, :G * D] = k.reshape(T, G * D).to(k_cache.dtype)
+    v_cache[loc, 0, :G * Dv] = v.to(v_cache.dtype)
+    return q.to(k_cache.dtype)
+
+
+def window_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, G: int, Dv: int, page_table: torch.Tensor, req_slots: torch.Tensor,
+                     seq_lens: torch.Tensor, q_lens: Optional[torch.Tensor], page_size: int, scale: float, softcap: float, window: int,
+                     slopes: Optional[torch.Tensor], sinks: Optional[torch.Tensor]) -> torch.Tensor:
+    """grouped-query attention over a paged cache with a tanh score cap, a per-head distance bias, a sliding window and soft-max sinks.
+
+    q [T, H, D]; caches [slots, 1, width] with the G key heads in the first ``G*D`` columns (values: ``G*Dv``); query head h reads key head
+    ``h // (H // G)``.  score_ij = cap(q_i . k_j * scale) - slopes_h * (i - j) with cap(s) = softcap * tanh(s / softcap) (``softcap <= 0``:
+    none); key j is visible when ``0 <= i - j < window`` (``window <= 0``: all earlier keys); ``sinks`` fp32 [H]: exp(sink_h) joins the
+    soft-max denominator only.  Returns fp32 [T, H, Dv]."""
+    T, H, D = q.shape
+    rep = H // G
+    out = torch.empty(T, H, Dv, dtype=torch.float32, device=q.device)
+    qs = 0
+    for b in range(req_slots.shape[0]):
+        L = int(seq_lens[b])
+        ql = 1 if q_lens is None else int(q_lens[b])
+        if ql <= 0:
+            continue
+        lo = 0 if window <= 0 else max(0, L - ql - window + 1)
+        pos = torch.arange(lo, L, device=q.device)
+        slots = page_table[int(req_slots[b]), (pos // page_size).long()].long() * page_size + pos % page_size
+        K = k_cache[slots, 0, :G * D].float().view(-1, G, D).repeat_interleave(rep, 1)
+        V = v_cache[slots, 0, :G * Dv].float().view(-1, G, Dv).repeat_interleave(rep, 1)
+        s = torch.einsum("qhd,khd->hqk", q[qs:qs + ql].float(), K) * scale
+        if softcap > 0:
+            s = softcap * torch.tanh(s / softcap)
+        qpos = torch.arange(L - ql, L, device=q.device)[:, None]
+        dist = (qpos - pos[None, :]).float()
+        if slopes is not None:
+            s = s - slopes.float()[:, None, None] * dist[None]
+        hide = dist < 0
+        if window > 0:
+            hide = hide | (dist >= window)
+        s = s.masked_fill(hide[None], float("-inf"))
+        if sinks is not None:
+            s = torch.cat([s, sinks.float()[:, None, None].expand(H, ql, 1)], -1)
+        p = torch.softmax(s, dim=-1)[..., : pos.numel()]
+        out[qs:qs + ql] = torch.einsum("hqk,khd->qhd", p, V)
+        qs += ql
+    return out
+
+
+def softmax_bias_route(logits: torch.Tensor, correction: Optional[torch.Tensor], top_k: int, n_real: int) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """soft-max router with a choice-only correction: s = softmax(logits) over all columns; the ``top_k`` largest ``s + correction`` are chosen,
+    weighted by their plain ``s`` (not renormalised).  Columns >= ``n_real`` are identity experts: their weights are summed into the third result.
+    -> (weights fp32 [T, top_k] with identity picks zeroed, ids int32 [T, top_k], identity weight fp32 [T])"""
+    s = torch.softmax(logits.float(), -1)
+    choice = s + correction.float() if correction is not None else s
+    ids = choice.topk(top_k, dim=-1).indices
+    w = s.gather(1, ids)
+    ident = ids >= n_real
+    return w.masked_fill(ident, 0.0).contiguous(), ids.to(torch.int32).contiguous(), (w * ident).sum(-1)
