@@ -272,6 +272,142 @@ void gated_delta_rule(const at::Tensor& u, int64_t Hk, int64_t Dk, int64_t H, in
   count();
 }
 
+// ---- bigram embedding / sandwich norms / Mamba-2 scan / biased window attention / identity-expert router
+static bool bf16_or_f32(const at::Tensor& t) { return t.scalar_type() == at::kBFloat16 || t.scalar_type() == at::kFloat; }
+
+void bigram_embedding(const at::Tensor& embed, c10::optional<at::Tensor> bigram, const at::Tensor& ids, c10::optional<at::Tensor> prev_tokens,
+                      c10::optional<at::Tensor> cu_q, const at::Tensor& req_slots, const at::Tensor& seq_lens, int64_t max_q_len, double scale,
+                      int64_t mul_prev, int64_t mul_cur, int64_t buckets, at::Tensor out) {
+  CHECK_CUDA(embed); CHECK_I32(ids); CHECK_I32(req_slots); CHECK_I32(seq_lens);
+  TORCH_CHECK(bf16_or_f32(embed) && embed.dim() == 2 && embed.is_contiguous() && ids.is_contiguous() && out.scalar_type() == at::kFloat &&
+              out.is_contiguous() && out.size(0) == ids.size(0) && out.size(1) == embed.size(1));
+  const int B = (int)req_slots.size(0);
+  if (cu_q.has_value()) { CHECK_I32(*cu_q); TORCH_CHECK(cu_q->numel() == B + 1); } else TORCH_CHECK(ids.size(0) == B);
+  if (bigram.has_value()) {
+    TORCH_CHECK(bigram->scalar_type() == embed.scalar_type() && bigram->is_contiguous() && bigram->size(1) == embed.size(1) && buckets > 0 &&
+                bigram->size(0) > buckets && prev_tokens.has_value() && prev_tokens->scalar_type() == at::kInt && prev_tokens->is_contiguous());
+  }
+  if (ids.size(0) == 0) return;
+  c10::cuda::CUDAGuard g(embed.device());
+  sglb::bigram_embedding(embed.data_ptr(), bigram.has_value() ? bigram->data_ptr() : nullptr, embed.scalar_type() == at::kBFloat16, ids.data_ptr<int>(),
+                         bigram.has_value() ? prev_tokens->data_ptr<int>() : nullptr, opt_ptr<int>(cu_q), req_slots.data_ptr<int>(),
+                         seq_lens.data_ptr<int>(), B, cu_q.has_value() ? (int)max_q_len : 1, (int)embed.size(1), (int)embed.size(0), (float)scale,
+                         (long long)mul_prev, (long long)mul_cur, (int)buckets, out.data_ptr<float>(), cur_stream());
+  count();
+}
+
+void postnorm_add_rmsnorm_f32(at::Tensor residual, const at::Tensor& delta, const at::Tensor& post_w, const at::Tensor& w, at::Tensor out, double eps) {
+  CHECK_CUDA(residual);
+  TORCH_CHECK(residual.scalar_type() == at::kFloat && residual.dim() == 2 && residual.is_contiguous() && out.is_contiguous() && w.is_contiguous() &&
+              post_w.is_contiguous() && delta.is_contiguous() && bf16_or_f32(out) && bf16_or_f32(delta));
+  TORCH_CHECK(out.scalar_type() == w.scalar_type() && out.scalar_type() == post_w.scalar_type() && out.numel() == residual.numel() &&
+              delta.numel() == residual.numel() && w.numel() == residual.size(1) && post_w.numel() == residual.size(1));
+  c10::cuda::CUDAGuard g(residual.device());
+  sglb::postnorm_add_rmsnorm_f32(residual.data_ptr<float>(), delta.data_ptr(), delta.scalar_type() == at::kBFloat16, post_w.data_ptr(), w.data_ptr(),
+                                 out.data_ptr(), out.scalar_type() == at::kBFloat16, (int)residual.size(0), (int)residual.size(1), (float)eps, cur_stream());
+  count();
+}
+
+void grouped_rmsnorm(const at::Tensor& x, const at::Tensor& w, int64_t groups, double eps, at::Tensor out) {
+  CHECK_CUDA(x);
+  TORCH_CHECK(x.scalar_type() == at::kFloat && x.dim() == 2 && x.is_contiguous() && out.is_contiguous() && w.is_contiguous() && bf16_or_f32(out) &&
+              out.scalar_type() == w.scalar_type() && out.numel() == x.numel() && w.numel() == x.size(1));
+  c10::cuda::CUDAGuard g(x.device());
+  sglb::grouped_rmsnorm(x.data_ptr<float>(), w.data_ptr(), out.data_ptr(), out.scalar_type() == at::kBFloat16, (int)x.size(0), (int)x.size(1), (int)groups,
+                        (float)eps, cur_stream());
+  count();
+}
+
+void mamba2_scan(const at::Tensor& u, c10::optional<at::Tensor> z, const at::Tensor& dt_raw, const at::Tensor& dt_bias, const at::Tensor& A_log,
+                 c10::optional<at::Tensor> D, at::Tensor state, const at::Tensor& req_slots, const at::Tensor& seq_lens, c10::optional<at::Tensor> cu_q,
+                 int64_t H, int64_t P, int64_t N, int64_t G, at::Tensor out) {
+  CHECK_CUDA(u); CHECK_I32(req_slots); CHECK_I32(seq_lens);
+  auto f32c = [](const at::Tensor& t) { return t.scalar_type() == at::kFloat && t.is_contiguous(); };
+  TORCH_CHECK(f32c(u) && f32c(dt_bias) && f32c(A_log) && f32c(state) && f32c(out) && u.dim() == 2 && u.size(1) >= H * P + 2 * G * N);
+  TORCH_CHECK(bf16_or_f32(dt_raw) && dt_raw.dim() == 2 && dt_raw.stride(1) == 1 && dt_raw.size(1) >= H && dt_raw.size(0) == u.size(0));
+  if (z.has_value()) TORCH_CHECK(z->scalar_type() == dt_raw.scalar_type() && z->dim() == 2 && z->stride(1) == 1 && z->size(1) >= H * P && z->size(0) == u.size(0));
+  if (D.has_value()) TORCH_CHECK(f32c(*D) && D->numel() == H);
+  TORCH_CHECK(state.dim() == 4 && state.size(1) == H && state.size(2) == N && state.size(3) == P && dt_bias.numel() == H && A_log.numel() == H &&
+              out.size(0) == u.size(0) && out.numel() == u.size(0) * H * P);
+  const int B = (int)req_slots.size(0);
+  if (cu_q.has_value()) { CHECK_I32(*cu_q); TORCH_CHECK(cu_q->numel() == B + 1); } else TORCH_CHECK(u.size(0) == B);
+  if (u.size(0) == 0) return;
+  c10::cuda::CUDAGuard g(u.device());
+  sglb::mamba2_scan(u.data_ptr<float>(), (int)u.stride(0), z.has_value() ? z->data_ptr() : nullptr, z.has_value() ? (int)z->stride(0) : 0,
+                    dt_raw.data_ptr(), (int)dt_raw.stride(0), dt_raw.scalar_type() == at::kBFloat16, dt_bias.data_ptr<float>(), A_log.data_ptr<float>(),
+                    opt_ptr<float>(D), state.data_ptr<float>(), req_slots.data_ptr<int>(), seq_lens.data_ptr<int>(), opt_ptr<int>(cu_q), B, (int)H, (int)P,
+                    (int)N, (int)G, out.data_ptr<float>(), cur_stream());
+  count();
+}
+
+void qk_norm_cache_write(const at::Tensor& qkv, int64_t H, int64_t G, int64_t D, int64_t Dv, const at::Tensor& positions, double eps, double temp_coef,
+                         int64_t temp_every, at::Tensor k_cache, at::Tensor v_cache, const at::Tensor& loc, bool normalise, at::Tensor q_out) {
+  CHECK_CUDA(qkv); CHECK_I32(positions); CHECK_I32(loc);
+  TORCH_CHECK(bf16_or_f32(qkv) && qkv.dim() == 2 && qkv.stride(1) == 1 && qkv.size(1) == (H + G) * D + G * Dv);
+  TORCH_CHECK(k_cache.scalar_type() == qkv.scalar_type() && v_cache.scalar_type() == qkv.scalar_type() && q_out.scalar_type() == qkv.scalar_type() &&
+              q_out.is_contiguous() && q_out.numel() == qkv.size(0) * H * D);
+  TORCH_CHECK(k_cache.dim() == 3 && k_cache.size(1) == 1 && k_cache.stride(2) == 1 && v_cache.stride(2) == 1 && k_cache.stride(0) == v_cache.stride(0) &&
+              k_cache.size(2) >= G * D && v_cache.size(2) >= G * Dv && temp_every >= 1 && positions.numel() == qkv.size(0) && loc.numel() == qkv.size(0));
+  if (qkv.size(0) == 0) return;
+  c10::cuda::CUDAGuard g(qkv.device());
+  sglb::qk_norm_cache_write(qkv.data_ptr(), (int)qkv.stride(0), qkv.scalar_type() == at::kBFloat16, (int)qkv.size(0), (int)H, (int)G, (int)D, (int)Dv,
+                            positions.data_ptr<int>(), (float)eps, (float)temp_coef, (int)temp_every, k_cache.data_ptr(), v_cache.data_ptr(),
+                            (size_t)k_cache.stride(0), loc.data_ptr<int>(), normalise, q_out.data_ptr(), cur_stream());
+  count();
+}
+
+void window_attention(const at::Tensor& q, const at::Tensor& k_cache, const at::Tensor& v_cache, int64_t G, int64_t Dv, const at::Tensor& page_table,
+                      const at::Tensor& req_slots, const at::Tensor& seq_lens, c10::optional<at::Tensor> cu_q, int64_t max_q_len, int64_t page_size,
+                      double scale, double softcap, int64_t window, c10::optional<at::Tensor> slopes, c10::optional<at::Tensor> sinks, at::Tensor out) {
+  CHECK_CUDA(q); CHECK_I32(page_table); CHECK_I32(req_slots); CHECK_I32(seq_lens);
+  TORCH_CHECK(bf16_or_f32(q) && q.dim() == 3 && q.is_contiguous() && out.is_contiguous() && out.scalar_type() == q.scalar_type() &&
+              out.numel() == q.size(0) * q.size(1) * Dv);
+  const int64_t H = q.size(1), D = q.size(2);
+  TORCH_CHECK(k_cache.scalar_type() == q.scalar_type() && v_cache.scalar_type() == q.scalar_type() && k_cache.dim() == 3 && k_cache.size(1) == 1 &&
+              k_cache.stride(2) == 1 && v_cache.stride(2) == 1 && k_cache.stride(0) == v_cache.stride(0) && k_cache.size(2) >= G * D &&
+              v_cache.size(2) >= G * Dv && page_table.dim() == 2 && page_table.stride(1) == 1 && G >= 1 && H % G == 0);
+  const int B = (int)req_slots.size(0);
+  if (cu_q.has_value()) { CHECK_I32(*cu_q); TORCH_CHECK(cu_q->numel() == B + 1); } else TORCH_CHECK(q.size(0) == B);
+  if (sinks.has_value()) TORCH_CHECK(sinks->scalar_type() == at::kFloat && sinks->is_contiguous() && sinks->numel() == H);
+  if (slopes.has_value()) TORCH_CHECK(slopes->scalar_type() == at::kFloat && slopes->is_contiguous() && slopes->numel() == H);
+  if (q.size(0) == 0) return;
+  c10::cuda::CUDAGuard g(q.device());
+  sglb::window_attention(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), q.scalar_type() == at::kBFloat16, (size_t)k_cache.stride(0), (int)H, (int)G,
+                         (int)D, (int)Dv, page_table.data_ptr<int>(), (int)page_table.stride(0), (int)page_size, req_slots.data_ptr<int>(),
+                         seq_lens.data_ptr<int>(), opt_ptr<int>(cu_q), B, cu_q.has_value() ? (int)max_q_len : 1, (float)scale, (float)softcap, (int)window,
+                         opt_ptr<float>(slopes), opt_ptr<float>(sinks), out.data_ptr(), cur_stream());
+  count();
+}
+
+void moe_softmax_bias_route(const at::Tensor& logits, c10::optional<at::Tensor> corr, int64_t n_real, at::Tensor w, at::Tensor ids, at::Tensor ident) {
+  CHECK_CUDA(logits); CHECK_I32(ids);
+  TORCH_CHECK(logits.scalar_type() == at::kFloat && logits.dim() == 2 && logits.stride(1) == 1 && w.scalar_type() == at::kFloat && w.is_contiguous() &&
+              ids.is_contiguous() && ident.scalar_type() == at::kFloat && ident.is_contiguous() && w.size(0) == logits.size(0) && ids.sizes() == w.sizes() &&
+              ident.numel() == logits.size(0));
+  if (corr.has_value()) TORCH_CHECK(corr->scalar_type() == at::kFloat && corr->is_contiguous() && corr->numel() == logits.size(1));
+  if (logits.size(0) == 0) return;
+  c10::cuda::CUDAGuard g(logits.device());
+  sglb::moe_softmax_bias_route(logits.data_ptr<float>(), (int)logits.stride(0), opt_ptr<float>(corr), (int)logits.size(0), (int)logits.size(1),
+                               (int)w.size(1), (int)n_real, w.data_ptr<float>(), ids.data_ptr<int>(), ident.data_ptr<float>(), cur_stream());
+  count();
+}
+
+void moe_identity_shared_combine(at::Tensor y, const at::Tensor& h, c10::optional<at::Tensor> ident, c10::optional<at::Tensor> shared,
+                                 c10::optional<at::Tensor> gate) {
+  CHECK_CUDA(y);
+  TORCH_CHECK(bf16_or_f32(y) && y.dim() == 2 && y.is_contiguous() && h.is_contiguous() && h.scalar_type() == y.scalar_type() && h.numel() == y.numel());
+  if (ident.has_value()) TORCH_CHECK(ident->scalar_type() == at::kFloat && ident->is_contiguous() && ident->numel() == y.size(0));
+  if (shared.has_value())
+    TORCH_CHECK(shared->scalar_type() == y.scalar_type() && shared->is_contiguous() && shared->numel() == y.numel() && gate.has_value() &&
+                gate->scalar_type() == at::kFloat && gate->is_contiguous() && gate->numel() == y.size(0));
+  if (y.size(0) == 0 || (!ident.has_value() && !shared.has_value())) return;
+  c10::cuda::CUDAGuard g(y.device());
+  sglb::moe_identity_shared_combine(y.data_ptr(), h.data_ptr(), opt_ptr<float>(ident), shared.has_value() ? shared->data_ptr() : nullptr,
+                                    shared.has_value() ? gate->data_ptr<float>() : nullptr, y.scalar_type() == at::kBFloat16, (int)y.size(0), (int)y.size(1),
+                                    cur_stream());
+  count();
+}
+
 void latent_attention(const at::Tensor& q, const at::Tensor& cache, int64_t rank, const at::Tensor& page_table, const at::Tensor& req_slots,
                       const at::Tensor& seq_lens, c10::optional<at::Tensor> cu_q, int64_t max_q_len, int64_t max_kv_len, int64_t page_size, double scale,
                       int64_t window, c10::optional<at::Tensor> sinks, at::Tensor out) {
@@ -713,6 +849,18 @@ TORCH_LIBRARY(sglb, m) {
   });
   m.def("add_rmsnorm_f32(Tensor(a!) residual, Tensor? delta, Tensor w, Tensor(b!) out, float eps, bool zero_centred) -> ()", &add_rmsnorm_f32);
   m.def("clamped_glu(Tensor gu, Tensor(a!) out, float limit, float alpha) -> ()", &clamped_glu);
+  m.def("bigram_embedding(Tensor embed, Tensor? bigram, Tensor ids, Tensor(a!)? prev_tokens, Tensor? cu_q, Tensor req_slots, Tensor seq_lens, "
+        "int max_q_len, float scale, int mul_prev, int mul_cur, int buckets, Tensor(b!) out) -> ()", &bigram_embedding);
+  m.def("postnorm_add_rmsnorm_f32(Tensor(a!) residual, Tensor delta, Tensor post_w, Tensor w, Tensor(b!) out, float eps) -> ()", &postnorm_add_rmsnorm_f32);
+  m.def("grouped_rmsnorm(Tensor x, Tensor w, int groups, float eps, Tensor(a!) out) -> ()", &grouped_rmsnorm);
+  m.def("mamba2_scan(Tensor u, Tensor? z, Tensor dt_raw, Tensor dt_bias, Tensor A_log, Tensor? D, Tensor(a!) state, Tensor req_slots, Tensor seq_lens, "
+        "Tensor? cu_q, int H, int P, int N, int G, Tensor(b!) out) -> ()", &mamba2_scan);
+  m.def("qk_norm_cache_write(Tensor qkv, int H, int G, int D, int Dv, Tensor positions, float eps, float temp_coef, int temp_every, "
+        "Tensor(a!) k_cache, Tensor(b!) v_cache, Tensor loc, bool normalise, Tensor(c!) q_out) -> ()", &qk_norm_cache_write);
+  m.def("window_attention(Tensor q, Tensor k_cache, Tensor v_cache, int G, int Dv, Tensor page_table, Tensor req_slots, Tensor seq_lens, Tensor? cu_q, "
+        "int max_q_len, int page_size, float scale, float softcap, int window, Tensor? slopes, Tensor? sinks, Tensor(a!) out) -> ()", &window_attention);
+  m.def("moe_softmax_bias_route(Tensor logits, Tensor? corr, int n_real, Tensor(a!) w, Tensor(b!) ids, Tensor(c!) ident) -> ()", &moe_softmax_bias_route);
+  m.def("moe_identity_shared_combine(Tensor(a!) y, Tensor h, Tensor? ident, Tensor? shared, Tensor? gate) -> ()", &moe_identity_shared_combine);
   m.def("gated_delta_rule(Tensor u, int Hk, int Dk, int H, int Dv, Tensor a_raw, Tensor A_log, Tensor dt_bias, Tensor b_raw, Tensor(a!) state, "
         "Tensor req_slots, Tensor seq_lens, Tensor? cu_q, Tensor? gate_raw, Tensor? norm_w, float eps, bool gate_silu, bool per_channel, Tensor(b!) out) -> ()",
         &gated_delta_rule);

@@ -108,6 +108,26 @@ void clamped_glu(const void* gu, void* out, bool bf16, int T, int I, float limit
 bool gated_delta_rule(const float* u, int ldu, int Hk, int Dk, int H, int Dv, const float* a_raw, bool per_channel, const float* A_log,
                       const float* dt_bias, const float* b_raw, const float* gate_raw, const float* norm_w, float eps, bool gate_silu, float* state,
                       const int* req_slots, const int* seq_lens, const int* cu_q, int B, float* out, cudaStream_t stream);
+// window_attention.cu
+void qk_norm_cache_write(const void* qkv, int ld, bool bf16, int T, int H, int G, int D, int Dv, const int* positions, float eps, float coef, int every,
+                         void* kc, void* vc, size_t ldc, const int* loc, bool normalise, void* q_out, cudaStream_t stream);
+void window_attention(const void* q, const void* kc, const void* vc, bool bf16, size_t ldc, int H, int G, int D, int Dv, const int* page_table,
+                      int pt_stride, int page_size, const int* req_slots, const int* seq_lens, const int* cu_q, int B, int max_q_len, float scale,
+                      float softcap, int window, const float* slopes, const float* sinks, void* out, cudaStream_t stream);
+// mamba.cu (ragged Mamba-2 recurrence), residual_f32.cu (sandwich norms), elementwise.cu (bigram embedding), moe.cu (identity / shared experts)
+void mamba2_scan(const float* u, int ldu, const void* z, int ldz, const void* dt_raw, int lddt, bool bf16, const float* dt_bias, const float* A_log,
+                 const float* D, float* state, const int* req_slots, const int* seq_lens, const int* cu_q, int B, int H, int P, int N, int G, float* out,
+                 cudaStream_t stream);
+void postnorm_add_rmsnorm_f32(float* residual, const void* delta, bool delta_bf16, const void* post_w, const void* w, void* out, bool out_bf16, int T,
+                              int H, float eps, cudaStream_t stream);
+void grouped_rmsnorm(const float* x, const void* w, void* out, bool out_bf16, int T, int C, int groups, float eps, cudaStream_t stream);
+void bigram_embedding(const void* embed, const void* bigram, bool bf16, const int* ids, int* prev_tokens, const int* cu_q, const int* req_slots,
+                      const int* seq_lens, int B, int max_q_len, int W, int vocab, float scale, long long mul_prev, long long mul_cur, int buckets,
+                      float* out, cudaStream_t stream);
+void moe_softmax_bias_route(const float* logits, int ld, const float* corr, int T, int E, int K, int n_real, float* w, int* ids, float* ident,
+                            cudaStream_t stream);
+void moe_identity_shared_combine(void* y, const void* h, const float* ident, const void* shared, const float* gate, bool bf16, int T, int W,
+                                 cudaStream_t stream);
 // latent_attention.cu
 void latent_attention(const float* q, const void* cache, bool cache_bf16, int ldc, int R, const int* page_table, int pt_stride, int page_size,
                       const int* req_slots, const int* seq_lens, const int* cu_q, int B, int max_q_len, int max_kv_len, int H, float scale,

@@ -377,4 +377,63 @@ void attn_fwd_simt(const void* q, const void* k_cache, const void* v_cache, void
   SGLB_CUDA_CHECK(cudaGetLastError());
 }
 
+// ---------------------------------------------------------------- token embedding + hashed bigram row, into the fp32 residual stream
+//   out[t] = embed[id_t] * scale + bigram[(id_(t-1) * mul_prev + id_t * mul_cur) mod buckets]      (a sequence's first token: row ``buckets``)
+// grid (chunks of 8 tokens, requests), threads over the width.  The token before a portion's first token is the request's state:
+// prev_tokens[slot].  The CTA that holds a portion's first token reads it and then stores the portion's last token there (no other CTA
+// touches that entry).
+template <typename T> __device__ __forceinline__ float be_ld(const T* p);
+template <> __device__ __forceinline__ float be_ld<float>(const float* p) { return *p; }
+template <> __device__ __forceinline__ float be_ld<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+
+template <typename T>
+__global__ void __launch_bounds__(256) bigram_embedding_kernel(const T* __restrict__ embed, const T* __restrict__ bigram, const int* __restrict__ ids,
+                                                               int* __restrict__ prev_tokens, const int* __restrict__ cu_q,
+                                                               const int* __restrict__ req_slots, const int* __restrict__ seq_lens, int W, int vocab,
+                                                               float scale, long long mul_prev, long long mul_cur, int buckets, float* __restrict__ out) {
+  __shared__ int s_prev;
+  const int b = blockIdx.y;
+  const int q0 = cu_q ? cu_q[b] : b;
+  const int n = cu_q ? cu_q[b + 1] - q0 : 1;
+  const int t0 = blockIdx.x * 8;
+  if (t0 >= n) return;
+  if (bigram && t0 == 0) {
+    if (threadIdx.x == 0) s_prev = (seq_lens[b] - n == 0) ? -1 : prev_tokens[req_slots[b]];
+    __syncthreads();
+    if (threadIdx.x == 0) prev_tokens[req_slots[b]] = ids[q0 + n - 1];
+  }
+  const int t1 = min(n, t0 + 8);
+  for (int t = t0; t < t1; ++t) {
+    int id = ids[q0 + t];
+    id = min(max(id, 0), vocab - 1);
+    const T* er = embed + (size_t)id * W;
+    const T* br = nullptr;
+    if (bigram) {
+      const int prev = t > 0 ? ids[q0 + t - 1] : s_prev;
+      long long row = buckets;
+      if (prev >= 0) {
+        row = ((long long)prev * mul_prev + (long long)id * mul_cur) % buckets;
+        if (row < 0) row += buckets;
+      }
+      br = bigram + (size_t)row * W;
+    }
+    float* o = out + (size_t)(q0 + t) * W;
+    for (int c = threadIdx.x; c < W; c += 256) o[c] = be_ld<T>(er + c) * scale + (br ? be_ld<T>(br + c) : 0.f);
+  }
+}
+
+void bigram_embedding(const void* embed, const void* bigram, bool bf16, const int* ids, int* prev_tokens, const int* cu_q, const int* req_slots,
+                      const int* seq_lens, int B, int max_q_len, int W, int vocab, float scale, long long mul_prev, long long mul_cur, int buckets,
+                      float* out, cudaStream_t stream) {
+  if (B <= 0 || max_q_len <= 0) return;
+  dim3 grid((max_q_len + 7) / 8, B);
+  if (bf16)
+    bigram_embedding_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)embed, (const __nv_bfloat16*)bigram, ids, prev_tokens, cu_q,
+                                                                     req_slots, seq_lens, W, vocab, scale, mul_prev, mul_cur, buckets, out);
+  else
+    bigram_embedding_kernel<float><<<grid, 256, 0, stream>>>((const float*)embed, (const float*)bigram, ids, prev_tokens, cu_q, req_slots, seq_lens, W,
+                                                             vocab, scale, mul_prev, mul_cur, buckets, out);
+  SGLB_CUDA_CHECK(cudaGetLastError());
+}
+
 }  // namespace sglb

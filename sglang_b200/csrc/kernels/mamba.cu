@@ -239,4 +239,156 @@ bool gated_delta_update(float* state, const int* req_slots, const float* u, int 
   return true;
 }
 
+// ---------------------------------------------------------------- Mamba-2 recurrence over a ragged batch (prompt portions and decode tokens alike)
+//   dt = softplus(dt_raw + dt_bias);  S <- exp(-exp(A_log) dt) S + dt B x^T;  y = S^T C + D x;  y <- y * silu(z)       (S fp32 [N, P] per head)
+// The columns of S (one per channel p of the head) never mix, so a CTA owns (request, head, a block of PC = 128 / KS columns) and walks the
+// request's tokens in order; a column lives in the registers of KS neighbouring lanes (ROWS rows each, row = r * KS + ks) and S^T C closes
+// with log2(KS) shuffles.  Tokens are staged 16 at a time: B, C, x, dt and the decay go to shared memory, then 16 recurrence steps run out of
+// shared memory (broadcast reads).  The state is read once and written once per call; a request whose cached length is zero starts from
+// S = 0 whatever its slot holds.  Token order is fixed, so a position's output is bit-identical however the prompt was cut or batched.
+// Reference counterpart: layers/attention/mamba/ops (chunked SSD scan for prompts, selective_state_update for decode).
+namespace {
+
+constexpr int M2_TC = 16;
+
+struct Mamba2Params {
+  const float* u; int ldu;                       // conv outputs [T, ldu] = [x (H*P) | B (G*N) | C (G*N)]
+  const void* z; int ldz;                        // gate rows (model dtype) or null
+  const void* dt_raw; int lddt;                  // [T, >= H] (model dtype)
+  const float* dt_bias; const float* A_log; const float* D;
+  float* state;                                  // [slots, H, N, P]
+  const int* req_slots; const int* seq_lens; const int* cu_q;
+  float* out;                                    // [T, H*P]
+  int H, P, N, G, pchunks;
+};
+
+__device__ __forceinline__ float m2_softplus(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+
+template <typename TZ, int ROWS, int KS>
+__global__ void __launch_bounds__(128) mamba2_scan_kernel(const Mamba2Params p) {
+  extern __shared__ float sm[];
+  constexpr int PC = 128 / KS;
+  const int b = blockIdx.y;
+  const int q0 = p.cu_q ? p.cu_q[b] : b;
+  const int n = p.cu_q ? p.cu_q[b + 1] - q0 : 1;
+  if (n <= 0) return;
+  const int h = blockIdx.x / p.pchunks, pc = blockIdx.x - h * p.pchunks;
+  const int H = p.H, P = p.P, N = p.N;
+  const int g = h / (H / p.G);
+  const int tid = threadIdx.x, col = tid / KS, ks = tid % KS;
+  const int pp = pc * PC + col;
+  const bool live = pp < P;
+  float* sB = sm;                      // [TC][N]
+  float* sC = sB + M2_TC * N;          // [TC][N]
+  float* sX = sC + M2_TC * N;          // [TC][PC]
+  float* sDt = sX + M2_TC * PC;        // [TC]
+  float* sDa = sDt + M2_TC;            // [TC]
+  float S[ROWS];
+  float* st = p.state + ((size_t)p.req_slots[b] * H + h) * N * P;
+  const bool fresh = p.seq_lens[b] - n == 0;
+#pragma unroll
+  for (int r = 0; r < ROWS; ++r) {
+    const int i = r * KS + ks;
+    S[r] = (live && !fresh && i < N) ? st[(size_t)i * P + pp] : 0.f;
+  }
+  const float a_exp = expf(p.A_log[h]);
+  const float dskip = p.D ? p.D[h] : 0.f;
+  const float dtb = p.dt_bias[h];
+  const TZ* zg = reinterpret_cast<const TZ*>(p.z);
+  const TZ* dg = reinterpret_cast<const TZ*>(p.dt_raw);
+  const int inner = H * P;
+  for (int t0 = 0; t0 < n; t0 += M2_TC) {
+    const int tc = min(M2_TC, n - t0);
+    for (int idx = tid; idx < tc * N; idx += 128) {
+      const int tt = idx / N, i = idx - tt * N;
+      const float* row = p.u + (size_t)(q0 + t0 + tt) * p.ldu + inner + g * N + i;
+      sB[tt * N + i] = row[0];
+      sC[tt * N + i] = row[p.G * N];
+    }
+    for (int idx = tid; idx < tc * PC; idx += 128) {
+      const int tt = idx / PC, c = idx - tt * PC;
+      sX[idx] = pc * PC + c < P ? p.u[(size_t)(q0 + t0 + tt) * p.ldu + h * P + pc * PC + c] : 0.f;
+    }
+    if (tid < tc) {
+      const float dt = m2_softplus(ld_f<TZ>(dg + (size_t)(q0 + t0 + tid) * p.lddt + h) + dtb);
+      sDt[tid] = dt;
+      sDa[tid] = expf(-a_exp * dt);
+    }
+    __syncthreads();
+    for (int tt = 0; tt < tc; ++tt) {
+      const float dt = sDt[tt], da = sDa[tt];
+      const float xv = sX[tt * PC + col];
+      const float dbx = dt * xv;
+      const float* bb = sB + tt * N;
+      const float* cc = sC + tt * N;
+      float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+      for (int r = 0; r < ROWS; ++r) {
+        const int i = r * KS + ks;
+        if (i < N) {
+          S[r] = S[r] * da + dbx * bb[i];
+          if (r & 1) a1 += S[r] * cc[i]; else a0 += S[r] * cc[i];
+        }
+      }
+      float acc = a0 + a1;
+#pragma unroll
+      for (int o = 1; o < KS; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      if (live && ks == 0) {
+        float y = acc + dskip * xv;
+        const size_t at = (size_t)(q0 + t0 + tt);
+        if (zg) {
+          const float zz = ld_f<TZ>(zg + at * p.ldz + h * P + pp);
+          y *= zz / (1.f + expf(-zz));
+        }
+        p.out[at * inner + h * P + pp] = y;
+      }
+    }
+    __syncthreads();
+  }
+  if (live) {
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+      const int i = r * KS + ks;
+      if (i < N) st[(size_t)i * P + pp] = S[r];
+    }
+  }
+}
+
+template <typename TZ, int ROWS, int KS>
+void launch_m2(Mamba2Params p, int B, cudaStream_t stream) {
+  constexpr int PC = 128 / KS;
+  p.pchunks = (p.P + PC - 1) / PC;
+  const size_t smem = sizeof(float) * ((size_t)M2_TC * p.N * 2 + (size_t)M2_TC * PC + 2 * M2_TC);
+  auto kern = mamba2_scan_kernel<TZ, ROWS, KS>;
+  if (smem > 48 * 1024) SGLB_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  kern<<<dim3(p.H * p.pchunks, B), 128, smem, stream>>>(p);
+  SGLB_CUDA_CHECK(cudaGetLastError());
+}
+
+template <typename TZ>
+void dispatch_m2(const Mamba2Params& p, int B, cudaStream_t stream) {
+  const int N = p.N;
+  if (N <= 16) launch_m2<TZ, 16, 1>(p, B, stream);
+  else if (N <= 32) launch_m2<TZ, 16, 2>(p, B, stream);
+  else if (N <= 64) launch_m2<TZ, 16, 4>(p, B, stream);
+  else if (N <= 128) launch_m2<TZ, 16, 8>(p, B, stream);
+  else if (N <= 256) launch_m2<TZ, 16, 16>(p, B, stream);
+  else if (N <= 512) launch_m2<TZ, 16, 32>(p, B, stream);
+  else launch_m2<TZ, 32, 32>(p, B, stream);
+}
+
+}  // namespace
+
+void mamba2_scan(const float* u, int ldu, const void* z, int ldz, const void* dt_raw, int lddt, bool bf16, const float* dt_bias, const float* A_log,
+                 const float* D, float* state, const int* req_slots, const int* seq_lens, const int* cu_q, int B, int H, int P, int N, int G, float* out,
+                 cudaStream_t stream) {
+  if (B <= 0) return;
+  if (N > 1024 || B > 65535 || H % G) throw std::runtime_error("sglb mamba2_scan: state size up to 1024, heads a multiple of groups");
+  Mamba2Params p;
+  p.u = u; p.ldu = ldu; p.z = z; p.ldz = ldz; p.dt_raw = dt_raw; p.lddt = lddt; p.dt_bias = dt_bias; p.A_log = A_log; p.D = D; p.state = state;
+  p.req_slots = req_slots; p.seq_lens = seq_lens; p.cu_q = cu_q; p.out = out; p.H = H; p.P = P; p.N = N; p.G = G; p.pchunks = 1;
+  if (bf16) dispatch_m2<__nv_bfloat16>(p, B, stream);
+  else dispatch_m2<float>(p, B, stream);
+}
+
 }  // namespace sglb

@@ -253,4 +253,101 @@ void moe_combine_push(const void* ys, const int* inv_pos, const float* pair_w, i
   SGLB_CUDA_CHECK(cudaGetLastError());
 }
 
+// ---------------------------------------------------------------- soft-max router with a choice-only correction and identity experts
+//   s = softmax(logits) over all E columns; the top_k largest (s + correction) are chosen and weighted by their plain s (not renormalised).
+//   Columns >= n_real are identity experts (they return their input): their chosen weights are summed into ident[t] and zeroed in w.
+// One warp per token; scores and choice values sit in shared memory; every pick is a warp arg-max (equal values: the lower index).
+__global__ void __launch_bounds__(128) moe_softmax_bias_route_kernel(const float* __restrict__ logits, int ld, const float* __restrict__ corr, int T, int E,
+                                                                     int K, int n_real, float* __restrict__ w, int* __restrict__ ids,
+                                                                     float* __restrict__ ident) {
+  extern __shared__ float rsm[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * 4 + warp;
+  if (t >= T) return;
+  float* sc = rsm + (size_t)warp * 2 * E;
+  float* ch = sc + E;
+  const float* row = logits + (size_t)t * ld;
+  float mx = -INFINITY;
+  for (int e = lane; e < E; e += 32) mx = fmaxf(mx, row[e]);
+  mx = warp_max(mx);
+  float sum = 0.f;
+  for (int e = lane; e < E; e += 32) {
+    const float v = expf(row[e] - mx);
+    sc[e] = v;
+    sum += v;
+  }
+  sum = warp_sum(sum);
+  const float inv = 1.f / sum;
+  for (int e = lane; e < E; e += 32) {
+    const float v = sc[e] * inv;
+    sc[e] = v;
+    ch[e] = v + (corr ? corr[e] : 0.f);
+  }
+  __syncwarp();
+  float idw = 0.f;
+  for (int k = 0; k < K; ++k) {
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int e = lane; e < E; e += 32)
+      if (ch[e] > best) { best = ch[e]; bi = e; }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+    }
+    if (lane == 0) {
+      const float sv = sc[bi];
+      const bool idn = bi >= n_real;
+      w[(size_t)t * K + k] = idn ? 0.f : sv;
+      ids[(size_t)t * K + k] = bi;
+      if (idn) idw += sv;
+      ch[bi] = -INFINITY;
+    }
+    __syncwarp();
+  }
+  if (lane == 0) ident[t] = idw;
+}
+
+void moe_softmax_bias_route(const float* logits, int ld, const float* corr, int T, int E, int K, int n_real, float* w, int* ids, float* ident,
+                            cudaStream_t stream) {
+  if (T <= 0) return;
+  if (E > 1024 || K > E) throw std::runtime_error("sglb moe_softmax_bias_route: at most 1024 router columns, top_k <= columns");
+  moe_softmax_bias_route_kernel<<<(T + 3) / 4, 128, sizeof(float) * 8 * E, stream>>>(logits, ld, corr, T, E, K, n_real, w, ids, ident);
+  SGLB_CUDA_CHECK(cudaGetLastError());
+}
+
+// y[t] += ident[t] * h[t] + sigmoid(gate[t]) * shared[t]   (identity experts and the always-on expert join the routed experts' sum), fp32 sums
+template <typename T> __device__ __forceinline__ float mc_ld(const T* p);
+template <> __device__ __forceinline__ float mc_ld<float>(const float* p) { return *p; }
+template <> __device__ __forceinline__ float mc_ld<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+template <typename T> __device__ __forceinline__ void mc_st(T* p, float v);
+template <> __device__ __forceinline__ void mc_st<float>(float* p, float v) { *p = v; }
+template <> __device__ __forceinline__ void mc_st<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16(v); }
+
+template <typename T>
+__global__ void __launch_bounds__(256) moe_identity_shared_combine_kernel(T* __restrict__ y, const T* __restrict__ h, const float* __restrict__ ident,
+                                                                          const T* __restrict__ shared, const float* __restrict__ gate, int W) {
+  const size_t base = (size_t)blockIdx.x * W;
+  const float iw = ident ? ident[blockIdx.x] : 0.f;
+  const float sg = shared ? 1.f / (1.f + expf(-gate[blockIdx.x])) : 0.f;
+  for (int c = threadIdx.x; c < W; c += 256) {
+    float v = mc_ld<T>(y + base + c);
+    if (ident) v += iw * mc_ld<T>(h + base + c);
+    if (shared) v += sg * mc_ld<T>(shared + base + c);
+    mc_st<T>(y + base + c, v);
+  }
+}
+
+void moe_identity_shared_combine(void* y, const void* h, const float* ident, const void* shared, const float* gate, bool bf16, int T, int W,
+                                 cudaStream_t stream) {
+  if (T <= 0) return;
+  if (bf16)
+    moe_identity_shared_combine_kernel<__nv_bfloat16><<<T, 256, 0, stream>>>((__nv_bfloat16*)y, (const __nv_bfloat16*)h, ident, (const __nv_bfloat16*)shared,
+                                                                             gate, W);
+  else
+    moe_identity_shared_combine_kernel<float><<<T, 256, 0, stream>>>((float*)y, (const float*)h, ident, (const float*)shared, gate, W);
+  SGLB_CUDA_CHECK(cudaGetLastError());
+}
+
 }  // namespace sglb

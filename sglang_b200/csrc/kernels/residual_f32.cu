@@ -80,7 +80,87 @@ __global__ void __launch_bounds__(256) clamped_glu_bf16x8_kernel(const __nv_bflo
   st128(out + (size_t)blockIdx.x * I + i, U4{o[0], o[1], o[2], o[3]});
 }
 
+// block-wide sum for 256 threads (every thread gets the total)
+__device__ __forceinline__ float block_sum_256(float v, float* red) {
+  v = warp_sum(v);
+  __syncthreads();                       // red may still be read from an earlier call
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float t = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) t += red[i];
+  return t;
+}
+
+// residual += rmsnorm(delta) * (1 + post_w);  out = rmsnorm(residual) * (1 + w): the post-norm of a branch, the residual add and the next
+// pre-norm of a sandwich-normed block in one pass over the row
+template <typename TD, typename TO>
+__global__ void __launch_bounds__(256) postnorm_add_rmsnorm_f32_kernel(float* __restrict__ res, const TD* __restrict__ delta, const TO* __restrict__ post_w,
+                                                                       const TO* __restrict__ w, TO* __restrict__ out, int H, float eps) {
+  __shared__ float red[8];
+  float* r = res + (size_t)blockIdx.x * H;
+  const TD* d = delta + (size_t)blockIdx.x * H;
+  float sd = 0.f;
+  for (int i = threadIdx.x; i < H; i += 256) {
+    const float v = ldf<TD>(d + i);
+    sd += v * v;
+  }
+  const float rd = 1.0f / sqrtf(block_sum_256(sd, red) / (float)H + eps);
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < H; i += 256) {
+    const float v = r[i] + ldf<TD>(d + i) * rd * (1.f + ldf<TO>(post_w + i));
+    r[i] = v;
+    ss += v * v;
+  }
+  const float rs = 1.0f / sqrtf(block_sum_256(ss, red) / (float)H + eps);
+  TO* o = out + (size_t)blockIdx.x * H;
+  for (int i = threadIdx.x; i < H; i += 256) stf<TO>(o + i, r[i] * rs * (1.f + ldf<TO>(w + i)));          // each thread re-reads what it wrote
+}
+
+// x fp32 [T, C] in ``groups`` equal parts: part / sqrt(mean(part^2) + eps) * w; grid (T, groups)
+template <typename TO>
+__global__ void __launch_bounds__(256) grouped_rmsnorm_kernel(const float* __restrict__ x, const TO* __restrict__ w, TO* __restrict__ out, int C, int per,
+                                                              float eps) {
+  __shared__ float red[8];
+  const size_t base = (size_t)blockIdx.x * C + (size_t)blockIdx.y * per;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < per; i += 256) {
+    const float v = x[base + i];
+    ss += v * v;
+  }
+  const float rs = 1.0f / sqrtf(block_sum_256(ss, red) / (float)per + eps);
+  for (int i = threadIdx.x; i < per; i += 256) stf<TO>(out + base + i, x[base + i] * rs * ldf<TO>(w + blockIdx.y * per + i));
+}
+
 }  // namespace
+
+void postnorm_add_rmsnorm_f32(float* residual, const void* delta, bool delta_bf16, const void* post_w, const void* w, void* out, bool out_bf16, int T,
+                              int H, float eps, cudaStream_t stream) {
+  if (T <= 0) return;
+  using bf = __nv_bfloat16;
+  if (out_bf16) {
+    if (delta_bf16)
+      postnorm_add_rmsnorm_f32_kernel<bf, bf><<<T, 256, 0, stream>>>(residual, (const bf*)delta, (const bf*)post_w, (const bf*)w, (bf*)out, H, eps);
+    else
+      postnorm_add_rmsnorm_f32_kernel<float, bf><<<T, 256, 0, stream>>>(residual, (const float*)delta, (const bf*)post_w, (const bf*)w, (bf*)out, H, eps);
+  } else {
+    if (delta_bf16)
+      postnorm_add_rmsnorm_f32_kernel<bf, float><<<T, 256, 0, stream>>>(residual, (const bf*)delta, (const float*)post_w, (const float*)w, (float*)out, H, eps);
+    else
+      postnorm_add_rmsnorm_f32_kernel<float, float><<<T, 256, 0, stream>>>(residual, (const float*)delta, (const float*)post_w, (const float*)w,
+                                                                           (float*)out, H, eps);
+  }
+  SGLB_CUDA_CHECK(cudaGetLastError());
+}
+
+void grouped_rmsnorm(const float* x, const void* w, void* out, bool out_bf16, int T, int C, int groups, float eps, cudaStream_t stream) {
+  if (T <= 0) return;
+  if (groups <= 0 || C % groups || groups > 65535) throw std::runtime_error("sglb grouped_rmsnorm: the width must split into equal parts");
+  dim3 g(T, groups);
+  if (out_bf16) grouped_rmsnorm_kernel<__nv_bfloat16><<<g, 256, 0, stream>>>(x, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, C, C / groups, eps);
+  else grouped_rmsnorm_kernel<float><<<g, 256, 0, stream>>>(x, (const float*)w, (float*)out, C, C / groups, eps);
+  SGLB_CUDA_CHECK(cudaGetLastError());
+}
 
 void add_rmsnorm_f32(float* residual, const void* delta, bool delta_bf16, const void* w, void* out, bool out_bf16, int T, int H, float eps,
                      bool zero_centred, cudaStream_t stream) {

@@ -1,0 +1,280 @@
+// Grouped-query attention over a paged cache whose scores carry the position: unit-RMS q / k, a query temperature that grows with the
+// position, a tanh score cap, a per-head distance bias, a sliding window and a soft-max sink per head.
+//
+//   qk_norm_cache_write : per token, every q and k head <- head / sqrt(mean(head^2) + eps); q also times 1 + coef * ln(floor((p + 1) / every) + 1);
+//                         k heads go to the first G*D columns of the key plane's row, v to the first G*Dv columns of the value plane's row.
+//   window_attention    : s_ij = cap * tanh(q_i . k_j * scale / cap) - slope_h * (i - j), visible for 0 <= i - j < window;
+//                         p_ij = exp(s_ij) / (exp(sink_h) + sum_j' exp(s_ij')); o_i = sum_j p_ij v_j.
+//
+// window_attention mapping: one CTA per (tile of queries, chunk of the heads that share a key head, request): 16 rows = QT queries x HC heads.
+// Key tiles of 64 positions are gathered through the page table into shared memory as fp32 (keys padded to a multiple of 4 columns, rows
+// offset by 4 floats so that 16-byte reads of neighbouring keys do not collide).  A warp owns 4 rows: for the scores a lane owns 2 keys and
+// reuses each 16-byte key read for its 4 rows; probabilities go through a warp-private shared tile; for the output a lane owns CV value
+// columns and reuses each value read for its 4 rows.  The online soft-max starts from (max = sink, sum = 1), which is the sink's term.
+// The same kernel serves prompt portions (ragged over cu_q) and decode tokens (cu_q == nullptr: one query per request).  All math is fp32;
+// the cache and q are bf16 or fp32.
+#include <stdexcept>
+
+#include "common.cuh"
+#include "tma_host.h"
+
+namespace sglb {
+namespace {
+
+template <typename T> __device__ __forceinline__ float wa_ld(const T* p);
+template <> __device__ __forceinline__ float wa_ld<float>(const float* p) { return *p; }
+template <> __device__ __forceinline__ float wa_ld<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+template <typename T> __device__ __forceinline__ void wa_st(T* p, float v);
+template <> __device__ __forceinline__ void wa_st<float>(float* p, float v) { *p = v; }
+template <> __device__ __forceinline__ void wa_st<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16(v); }
+
+template <typename T>
+__global__ void __launch_bounds__(128) qk_norm_cache_write_kernel(const T* __restrict__ qkv, int ld, int H, int G, int D, int Dv,
+                                                                  const int* __restrict__ positions, float eps, float coef, int every,
+                                                                  T* __restrict__ kc, T* __restrict__ vc, size_t ldc, const int* __restrict__ loc,
+                                                                  int normalise, T* __restrict__ q_out) {
+  const int t = blockIdx.x;
+  const T* row = qkv + (size_t)t * ld;
+  const size_t slot = (size_t)loc[t];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float temp = 1.f;
+  if (coef != 0.f) temp = 1.f + coef * logf((float)((positions[t] + 1) / every) + 1.f);
+  for (int hd = warp; hd < H + G; hd += 4) {
+    const T* src = row + (size_t)hd * D;
+    float ss = 0.f;
+    for (int i = lane; i < D; i += 32) {
+      const float v = wa_ld<T>(src + i);
+      ss += v * v;
+    }
+    ss = warp_sum(ss);
+    float mult = normalise ? 1.0f / sqrtf(ss / (float)D + eps) : 1.f;
+    T* dst;
+    if (hd < H) {
+      dst = q_out + ((size_t)t * H + hd) * D;
+      mult *= temp;
+    } else {
+      dst = kc + slot * ldc + (size_t)(hd - H) * D;
+    }
+    for (int i = lane; i < D; i += 32) wa_st<T>(dst + i, wa_ld<T>(src + i) * mult);
+  }
+  const T* vs = row + (size_t)(H + G) * D;
+  T* vd = vc + slot * ldc;
+  for (int i = threadIdx.x; i < G * Dv; i += 128) vd[i] = vs[i];
+}
+
+constexpr int WA_KT = 64;        // keys per tile
+constexpr int WA_ROWS = 16;      // (query, head) rows per CTA: 4 warps x 4 rows
+
+struct WinAttnParams {
+  const void* q; const void* kc; const void* vc; void* out;
+  size_t ldc;                                  // elements between cache rows
+  const int* page_table; int pt_stride; int page_size;
+  const int* req_slots; const int* seq_lens; const int* cu_q;
+  const float* slopes; const float* sinks;
+  int H, G, HG, HC, nchunks, QT, D, Dp, Dv;
+  float scale, softcap; int window;
+};
+
+template <typename T, int CV>
+__global__ void __launch_bounds__(128) window_attention_kernel(const WinAttnParams p) {
+  extern __shared__ __align__(16) float smem[];
+  const int b = blockIdx.z;
+  const int q0 = p.cu_q ? p.cu_q[b] : b;
+  const int n = p.cu_q ? p.cu_q[b + 1] - q0 : 1;
+  const int qt0 = blockIdx.x * p.QT;
+  if (qt0 >= n) return;
+  const int nq = min(p.QT, n - qt0);
+  const int L = p.seq_lens[b];
+  const int pos0 = L - n + qt0;                         // position of the tile's first query
+  const int g = blockIdx.y / p.nchunks, chunk = blockIdx.y - g * p.nchunks;
+  const int hbase = g * p.HG + chunk * p.HC;            // first head of this CTA
+  const int nh = min(p.HC, p.HG - chunk * p.HC);        // heads of this CTA
+  const int D = p.D, Dp = p.Dp, Dv = p.Dv, HC = p.HC;
+  const int ldk = Dp + 4, ldv = 32 * CV;
+  float* sQ = smem;                                     // [16][Dp]
+  float* sK = sQ + WA_ROWS * Dp;                        // [64][Dp + 4]
+  float* sV = sK + WA_KT * ldk;                         // [64][32 * CV]
+  float* sP = sV + WA_KT * ldv;                         // [16][64]
+  int* sSlot = reinterpret_cast<int*>(sP + WA_ROWS * WA_KT);   // [64]
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const T* qg = reinterpret_cast<const T*>(p.q);
+  const T* kg = reinterpret_cast<const T*>(p.kc);
+  const T* vg = reinterpret_cast<const T*>(p.vc);
+  // ---- queries (times the score scale), zero rows where the tile has no query or head
+  for (int idx = tid; idx < WA_ROWS * Dp; idx += 128) {
+    const int r = idx / Dp, d = idx - r * Dp;
+    const int qi = r / HC, hc = r - qi * HC;
+    float v = 0.f;
+    if (qi < nq && hc < nh && d < D) v = wa_ld<T>(qg + ((size_t)(q0 + qt0 + qi) * p.H + hbase + hc) * D + d) * p.scale;
+    sQ[idx] = v;
+  }
+  // ---- per-row constants and online soft-max state (the sink is the first term: max = sink, sum = 1)
+  const int r0 = warp * 4;
+  float m[4], l[4], slope[4], O[4][CV];
+  int qpos[4];
+  bool rowok[4];
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    const int qi = (r0 + r) / HC, hc = (r0 + r) - qi * HC;
+    rowok[r] = qi < nq && hc < nh;
+    const int h = hbase + (rowok[r] ? hc : 0);
+    qpos[r] = pos0 + qi;
+    slope[r] = p.slopes ? p.slopes[h] : 0.f;
+    m[r] = p.sinks ? p.sinks[h] : -INFINITY;
+    l[r] = p.sinks ? 1.f : 0.f;
+#pragma unroll
+    for (int c = 0; c < CV; ++c) O[r][c] = 0.f;
+  }
+  const int klo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+  const int khi = pos0 + nq;                            // one past the last key any query of the tile sees
+  const int* pt = p.page_table + (size_t)p.req_slots[b] * p.pt_stride;
+  const float inv_cap = p.softcap > 0.f ? 1.f / p.softcap : 0.f;
+  for (int kt = klo; kt < khi; kt += WA_KT) {
+    __syncthreads();                                    // everyone is done with the previous tile (and sQ is written)
+    if (tid < WA_KT) {
+      const int j = kt + tid;
+      sSlot[tid] = j < khi ? pt[j / p.page_size] * p.page_size + j % p.page_size : -1;
+    }
+    __syncthreads();
+    for (int idx = tid; idx < WA_KT * Dp; idx += 128) {
+      const int jj = idx / Dp, d = idx - jj * Dp;
+      const int s = sSlot[jj];
+      sK[jj * ldk + d] = (s >= 0 && d < D) ? wa_ld<T>(kg + (size_t)s * p.ldc + (size_t)g * D + d) : 0.f;
+    }
+    for (int idx = tid; idx < WA_KT * ldv; idx += 128) {
+      const int jj = idx / ldv, c = idx - jj * ldv;
+      const int s = sSlot[jj];
+      sV[idx] = (s >= 0 && c < Dv) ? wa_ld<T>(vg + (size_t)s * p.ldc + (size_t)g * Dv + c) : 0.f;
+    }
+    __syncthreads();
+    // ---- scores: lane owns keys lane and lane + 32, for the warp's 4 rows
+    float acc[2][4];
+#pragma unroll
+    for (int kk = 0; kk < 2; ++kk)
+#pragma unroll
+      for (int r = 0; r < 4; ++r) acc[kk][r] = 0.f;
+    const float* k0p = sK + lane * ldk;
+    const float* k1p = sK + (lane + 32) * ldk;
+    for (int d = 0; d < Dp; d += 4) {
+      const float4 ka = *reinterpret_cast<const float4*>(k0p + d);
+      const float4 kb = *reinterpret_cast<const float4*>(k1p + d);
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const float4 qv = *reinterpret_cast<const float4*>(sQ + (r0 + r) * Dp + d);
+        acc[0][r] += qv.x * ka.x + qv.y * ka.y + qv.z * ka.z + qv.w * ka.w;
+        acc[1][r] += qv.x * kb.x + qv.y * kb.y + qv.z * kb.z + qv.w * kb.w;
+      }
+    }
+    // ---- cap, distance bias, mask, online soft-max
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      float s[2];
+#pragma unroll
+      for (int kk = 0; kk < 2; ++kk) {
+        const int j = kt + lane + 32 * kk;
+        const int dist = qpos[r] - j;
+        float v = acc[kk][r];
+        if (p.softcap > 0.f) v = p.softcap * tanhf(v * inv_cap);
+        v -= slope[r] * (float)dist;
+        const bool vis = rowok[r] && dist >= 0 && (p.window <= 0 || dist < p.window);
+        s[kk] = vis ? v : -INFINITY;
+      }
+      const float mt = warp_max(fmaxf(s[0], s[1]));
+      const float mn = fmaxf(m[r], mt);
+      const float corr = (m[r] == -INFINITY) ? 0.f : __expf(m[r] - mn);
+      const float p0 = (s[0] == -INFINITY) ? 0.f : __expf(s[0] - mn);
+      const float p1 = (s[1] == -INFINITY) ? 0.f : __expf(s[1] - mn);
+      l[r] = l[r] * corr + warp_sum(p0 + p1);
+      m[r] = mn;
+#pragma unroll
+      for (int c = 0; c < CV; ++c) O[r][c] *= corr;
+      sP[(r0 + r) * WA_KT + lane] = p0;
+      sP[(r0 + r) * WA_KT + lane + 32] = p1;
+    }
+    __syncwarp();
+    // ---- output: lane owns value columns lane + 32 c
+    const int jn = min(WA_KT, khi - kt);
+    for (int jj = 0; jj < jn; jj += 4) {
+      float4 pr[4];
+#pragma unroll
+      for (int r = 0; r < 4; ++r) pr[r] = *reinterpret_cast<const float4*>(sP + (r0 + r) * WA_KT + jj);
+#pragma unroll
+      for (int c = 0; c < CV; ++c) {
+        const float v0 = sV[(jj + 0) * ldv + lane + 32 * c], v1 = sV[(jj + 1) * ldv + lane + 32 * c];
+        const float v2 = sV[(jj + 2) * ldv + lane + 32 * c], v3 = sV[(jj + 3) * ldv + lane + 32 * c];
+#pragma unroll
+        for (int r = 0; r < 4; ++r) O[r][c] += pr[r].x * v0 + pr[r].y * v1 + pr[r].z * v2 + pr[r].w * v3;
+      }
+    }
+    __syncwarp();
+  }
+  T* og = reinterpret_cast<T*>(p.out);
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    if (!rowok[r]) continue;
+    const int qi = (r0 + r) / HC, hc = (r0 + r) - qi * HC;
+    const float inv = l[r] > 0.f ? 1.f / l[r] : 0.f;
+    T* dst = og + ((size_t)(q0 + qt0 + qi) * p.H + hbase + hc) * Dv;
+#pragma unroll
+    for (int c = 0; c < CV; ++c) {
+      const int col = lane + 32 * c;
+      if (col < Dv) wa_st<T>(dst + col, O[r][c] * inv);
+    }
+  }
+}
+
+template <typename T, int CV>
+void launch_wa(const WinAttnParams& p, int B, int max_q_len, cudaStream_t stream) {
+  const size_t smem = sizeof(float) * ((size_t)WA_ROWS * p.Dp + (size_t)WA_KT * (p.Dp + 4) + (size_t)WA_KT * 32 * CV + (size_t)WA_ROWS * WA_KT) +
+                      sizeof(int) * WA_KT;
+  auto kern = window_attention_kernel<T, CV>;
+  if (smem > 48 * 1024) SGLB_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  dim3 grid((max_q_len + p.QT - 1) / p.QT, p.G * p.nchunks, B);
+  kern<<<grid, 128, smem, stream>>>(p);
+  SGLB_CUDA_CHECK(cudaGetLastError());
+}
+
+template <typename T>
+void dispatch_wa(const WinAttnParams& p, int B, int max_q_len, cudaStream_t stream) {
+  const int cv = (p.Dv + 31) / 32;
+  if (cv <= 1) launch_wa<T, 1>(p, B, max_q_len, stream);
+  else if (cv <= 2) launch_wa<T, 2>(p, B, max_q_len, stream);
+  else if (cv <= 4) launch_wa<T, 4>(p, B, max_q_len, stream);
+  else launch_wa<T, 8>(p, B, max_q_len, stream);
+}
+
+}  // namespace
+
+void qk_norm_cache_write(const void* qkv, int ld, bool bf16, int T, int H, int G, int D, int Dv, const int* positions, float eps, float coef, int every,
+                         void* kc, void* vc, size_t ldc, const int* loc, bool normalise, void* q_out, cudaStream_t stream) {
+  if (T <= 0) return;
+  if (bf16)
+    qk_norm_cache_write_kernel<__nv_bfloat16><<<T, 128, 0, stream>>>((const __nv_bfloat16*)qkv, ld, H, G, D, Dv, positions, eps, coef, every,
+                                                                     (__nv_bfloat16*)kc, (__nv_bfloat16*)vc, ldc, loc, normalise ? 1 : 0, (__nv_bfloat16*)q_out);
+  else
+    qk_norm_cache_write_kernel<float><<<T, 128, 0, stream>>>((const float*)qkv, ld, H, G, D, Dv, positions, eps, coef, every, (float*)kc, (float*)vc, ldc,
+                                                             loc, normalise ? 1 : 0, (float*)q_out);
+  SGLB_CUDA_CHECK(cudaGetLastError());
+}
+
+void window_attention(const void* q, const void* kc, const void* vc, bool bf16, size_t ldc, int H, int G, int D, int Dv, const int* page_table,
+                      int pt_stride, int page_size, const int* req_slots, const int* seq_lens, const int* cu_q, int B, int max_q_len, float scale,
+                      float softcap, int window, const float* slopes, const float* sinks, void* out, cudaStream_t stream) {
+  if (B <= 0 || max_q_len <= 0) return;
+  if (D > 256 || Dv > 256 || B > 65535 || H % G) throw std::runtime_error("sglb window_attention: head sizes up to 256, heads a multiple of key heads");
+  WinAttnParams p;
+  p.q = q; p.kc = kc; p.vc = vc; p.out = out; p.ldc = ldc;
+  p.page_table = page_table; p.pt_stride = pt_stride; p.page_size = page_size;
+  p.req_slots = req_slots; p.seq_lens = seq_lens; p.cu_q = cu_q; p.slopes = slopes; p.sinks = sinks;
+  p.H = H; p.G = G; p.HG = H / G;
+  p.HC = std::min(p.HG, WA_ROWS);
+  p.nchunks = (p.HG + p.HC - 1) / p.HC;
+  p.QT = std::max(1, WA_ROWS / p.HC);
+  p.D = D; p.Dp = (D + 3) / 4 * 4; p.Dv = Dv;
+  p.scale = scale; p.softcap = softcap; p.window = window;
+  if (p.G * p.nchunks > 65535) throw std::runtime_error("sglb window_attention: too many heads for one launch");
+  if (bf16) dispatch_wa<__nv_bfloat16>(p, B, max_q_len, stream);
+  else dispatch_wa<float>(p, B, max_q_len, stream);
+}
+
+}  // namespace sglb

@@ -122,7 +122,7 @@ class IdentitySharedMoE(nn.Module):
         y = self.experts.forward_routed(h, w, ids)                             # identity picks carry weight 0 and an id no expert owns
         y = y.resolve() if hasattr(y, "resolve") else y
         sh = self.shared(h) if self.shared is not None else None
-        return moe_ops.moe_combine(y.contiguous(), h, ident if self.n_id else None, sh, z[:, n] if sh is not None else None)
+        return moe_ops.moe_identity_shared_combine(y.contiguous(), h, ident if self.n_id else None, sh, z[:, n] if sh is not None else None)
 
 
 class ZaparaxBlock(nn.Module):

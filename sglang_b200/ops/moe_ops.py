@@ -93,12 +93,15 @@ def softmax_bias_route(logits: torch.Tensor, correction, top_k: int, n_real: int
     return torch_ref.softmax_bias_route(logits, correction, top_k, n_real)
 
 
-def moe_combine(y: torch.Tensor, h: torch.Tensor, ident_w, shared, shared_logit) -> torch.Tensor:
+def moe_identity_shared_combine(y: torch.Tensor, h: torch.Tensor, ident_w, shared, shared_logit) -> torch.Tensor:
     """y + ident_w * h + sigmoid(shared_logit) * shared, rows of [T, width] (identity experts return their input; the always-on expert is gated
     by one number per token); fp32 sums (csrc/kernels/moe.cu)"""
-    if y.is_cuda and _has("moe_combine") and y.dtype in (torch.bfloat16, torch.float32) and y.is_contiguous() and h.is_contiguous() and h.dtype == y.dtype \
-            and (shared is None or (shared.is_contiguous() and shared.dtype == y.dtype and shared_logit is not None and shared_logit.stride(0) >= 1)):
-        torch.ops.sglb.moe_combine(y, h, ident_w, shared, None if shared is None else shared_logit.float().contiguous())
+    if ident_w is None and shared is None:
+        return y
+    if y.is_cuda and _has("moe_identity_shared_combine") and y.dtype in (torch.bfloat16, torch.float32) and y.is_contiguous() and h.is_contiguous() \
+            and h.dtype == y.dtype and (shared is None or (shared.is_contiguous() and shared.dtype == y.dtype)):
+        torch.ops.sglb.moe_identity_shared_combine(y, h, None if ident_w is None else ident_w.float().contiguous(), shared,
+                                                   None if shared is None else shared_logit.float().contiguous())
         return y
     out = y.float()
     if ident_w is not None:

@@ -1,0 +1,261 @@
+"""Zaparax CUDA kernels against their fp32 PyTorch references (``ops/torch_ref.py``) and the engine on CUDA against the plain oracle."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from sglang_b200 import ops
+from sglang_b200.ops import moe_ops, torch_ref
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+
+
+def _need():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+    assert ops.load_native(), "the CUDA extension must be built on a GPU box"
+
+
+def _i32(x, dev=DEV):
+    return torch.tensor(x, dtype=torch.int32, device=dev)
+
+
+def _ragged(q_lens, cached):
+    cu = np.concatenate([[0], np.cumsum(q_lens)])
+    seq = [c + q for c, q in zip(cached, q_lens)]
+    return cu.tolist(), seq
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_bigram_embedding(dtype):
+    _need()
+    g = torch.Generator().manual_seed(0)
+    V, W, NB = 97, 40, 53
+    emb, bg = torch.randn(V, W, generator=g).to(dtype), torch.randn(NB + 1, W, generator=g).to(dtype)
+    q_lens, cached = [1, 19, 3, 9], [5, 0, 0, 7]
+    cu, seq = _ragged(q_lens, cached)
+    ids = torch.randint(0, V, (sum(q_lens),), generator=g).int()
+    slots = [3, 1, 4, 2]
+    prev = torch.randint(0, V, (6,), generator=g).int()
+    p1, p2 = prev.clone(), prev.clone().to(DEV)
+    ref = torch_ref.bigram_embedding(emb, bg, ids, p1, _i32(cu, "cpu"), _i32(slots, "cpu"), _i32(seq, "cpu"), 3.0, 31, 7, NB)
+    got = ops.bigram_embedding(emb.to(DEV), bg.to(DEV), ids.to(DEV), p2, _i32(cu), _i32(slots), _i32(seq), max(q_lens), 3.0, 31, 7, NB)
+    torch.testing.assert_close(got.cpu(), ref, rtol=1e-6, atol=1e-6)
+    assert torch.equal(p2.cpu(), p1)
+    # decode form (one token per request, no cu_q) and no bigram table
+    ids1 = ids[:4].contiguous()
+    ref = torch_ref.bigram_embedding(emb, bg, ids1, p1, None, _i32(slots, "cpu"), _i32([9, 2, 1, 8], "cpu"), 3.0, 31, 7, NB)
+    got = ops.bigram_embedding(emb.to(DEV), bg.to(DEV), ids1.to(DEV), p2, None, _i32(slots), _i32([9, 2, 1, 8]), 1, 3.0, 31, 7, NB)
+    torch.testing.assert_close(got.cpu(), ref, rtol=1e-6, atol=1e-6)
+    assert torch.equal(p2.cpu(), p1)
+    got = ops.bigram_embedding(emb.to(DEV), None, ids1.to(DEV), None, None, _i32(slots), _i32([9, 2, 1, 8]), 1, 0.5)
+    torch.testing.assert_close(got.cpu(), emb[ids1.long()].float() * 0.5)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("W", [24, 256, 1000])
+def test_sandwich_norm_and_grouped_norm(dtype, W):
+    _need()
+    g = torch.Generator().manual_seed(1)
+    T = 13
+    res = torch.randn(T, W, generator=g) * 3
+    delta = (torch.randn(T, W, generator=g) * 5).to(dtype)
+    pw, w = (torch.randn(W, generator=g) * 0.2).to(dtype), (torch.randn(W, generator=g) * 0.2).to(dtype)
+    r1, r2 = res.clone(), res.clone().to(DEV)
+    ref = torch_ref.postnorm_add_rmsnorm_f32(r1, delta, pw, w, 1e-5, dtype)
+    got = ops.add_rmsnorm_f32(r2, delta.to(DEV), w.to(DEV), 1e-5, True, dtype, pw.to(DEV))
+    torch.testing.assert_close(r2.cpu(), r1, rtol=1e-5, atol=1e-5)
+    torch.testing.assert_close(got.cpu().float(), ref.float(), rtol=1e-2 if dtype == torch.bfloat16 else 1e-5, atol=1e-2 if dtype == torch.bfloat16 else 1e-5)
+    for groups in (1, 2, 4, 8):
+        if W % groups:
+            continue
+        x = torch.randn(T, W, generator=g) * 2
+        ref = torch_ref.grouped_rmsnorm(x, w, groups, 1e-5, dtype)
+        got = ops.grouped_rmsnorm(x.to(DEV), w.to(DEV), groups, 1e-5, dtype)
+        torch.testing.assert_close(got.cpu().float(), ref.float(), rtol=1e-2 if dtype == torch.bfloat16 else 1e-5, atol=1e-2 if dtype == torch.bfloat16 else 1e-5)
+
+
+@pytest.mark.parametrize("H,P,N,G", [(8, 32, 32, 2), (3, 5, 7, 1), (4, 64, 128, 4), (2, 130, 16, 2), (6, 24, 200, 3), (1, 8, 600, 1)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_mamba2_scan(H, P, N, G, dtype):
+    _need()
+    g = torch.Generator().manual_seed(2)
+    q_lens, cached = [37, 1, 2, 18], [0, 11, 0, 40]
+    cu, seq = _ragged(q_lens, cached)
+    T, inner = sum(q_lens), H * P
+    u = torch.randn(T, inner + 2 * G * N, generator=g)
+    proj = torch.randn(T, inner + 3 + H, generator=g).to(dtype)          # [z | 3 unused columns | dt]: strided views like the mixer's
+    z, dt_raw = proj[:, :inner], proj[:, inner + 3:]
+    dtb, A_log, D = torch.randn(H, generator=g) - 1.0, torch.randn(H, generator=g) * 0.5 - 1.0, torch.randn(H, generator=g)
+    state = torch.randn(6, H, N, P, generator=g)
+    slots = [2, 5, 0, 3]
+    s1, s2 = state.clone(), state.clone().to(DEV)
+    ref = torch_ref.mamba2_scan(u, z, dt_raw, dtb, A_log, D, s1, _i32(slots, "cpu"), _i32(seq, "cpu"), _i32(q_lens, "cpu"), H, P, N, G)
+    pd = proj.to(DEV)
+    got = ops.mamba2_scan(u.to(DEV), pd[:, :inner], pd[:, inner + 3:], dtb.to(DEV), A_log.to(DEV), D.to(DEV), s2, _i32(slots), _i32(seq), _i32(cu),
+                          _i32(q_lens), H, P, N, G)
+    torch.testing.assert_close(got.cpu(), ref, rtol=2e-4, atol=2e-4)
+    torch.testing.assert_close(s2.cpu(), s1, rtol=2e-4, atol=2e-4)
+    # decode form continues from the states just written
+    u1 = torch.randn(4, inner + 2 * G * N, generator=g)
+    p1 = torch.randn(4, inner + 3 + H, generator=g).to(dtype)
+    seq1 = [s + 1 for s in seq]
+    ref = torch_ref.mamba2_scan(u1, p1[:, :inner], p1[:, inner + 3:], dtb, A_log, None, s1, _i32(slots, "cpu"), _i32(seq1, "cpu"), None, H, P, N, G)
+    pd = p1.to(DEV)
+    got = ops.mamba2_scan(u1.to(DEV), pd[:, :inner], pd[:, inner + 3:], dtb.to(DEV), A_log.to(DEV), None, s2, _i32(slots), _i32(seq1), None, None, H, P, N, G)
+    torch.testing.assert_close(got.cpu(), ref, rtol=2e-4, atol=2e-4)
+    torch.testing.assert_close(s2.cpu(), s1, rtol=2e-4, atol=2e-4)
+
+
+def _paged(n_req, max_len, ps, width, dtype, g):
+    pages_per = (max_len + ps - 1) // ps
+    n_pages = n_req * pages_per + 3
+    perm = torch.randperm(n_pages - 1, generator=g)[: n_req * pages_per] + 1
+    pt = torch.zeros(n_req + 2, pages_per + 1, dtype=torch.int32)
+    for r in range(n_req):
+        pt[r + 1, :pages_per] = perm[r * pages_per:(r + 1) * pages_per].int()
+    kc = (torch.randn(n_pages * ps, 1, width, generator=g)).to(dtype)
+    vc = (torch.randn(n_pages * ps, 1, width, generator=g)).to(dtype)
+    return pt, kc, vc
+
+
+@pytest.mark.parametrize("H,G,D,Dv,window,cap", [(8, 1, 64, 64, 96, 50.0), (6, 2, 10, 7, 5, 3.0), (4, 4, 32, 48, -1, 0.0), (32, 1, 16, 16, 33, 20.0),
+                                                 (3, 3, 128, 128, 70, 10.0), (2, 1, 200, 256, 17, 0.0)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_window_attention_and_cache_write(H, G, D, Dv, window, cap, dtype):
+    _need()
+    g = torch.Generator().manual_seed(3)
+    ps = 16
+    q_lens, cached = [45, 1, 2, 130], [100, 77, 0, 0]
+    cu, seq = _ragged(q_lens, cached)
+    T = sum(q_lens)
+    width = G * max(D, Dv) + 8
+    pt, kc, vc = _paged(4, max(seq), ps, width, dtype, g)
+    slots = [1, 2, 3, 4]
+    pos = torch.cat([torch.arange(c, c + q) for c, q in zip(cached, q_lens)]).int()
+    req = torch.cat([torch.full((q,), s) for s, q in zip(slots, q_lens)])
+    loc = (pt[req.long(), (pos // ps).long()] * ps + pos % ps).int()
+    qkv = torch.randn(T, (H + G) * D + G * Dv, generator=g).to(dtype)
+    k1, v1 = kc.clone(), vc.clone()
+    k2, v2 = kc.clone().to(DEV), vc.clone().to(DEV)
+    q_ref = torch_ref.qk_norm_cache_write(qkv, H, G, D, Dv, pos, 1e-5, 0.5, 16, k1, v1, loc)
+    q_got = ops.qk_norm_cache_write(qkv.to(DEV), H, G, D, Dv, pos.to(DEV), 1e-5, 0.5, 16, k2, v2, loc.to(DEV))
+    tol = dict(rtol=2e-2, atol=2e-2) if dtype == torch.bfloat16 else dict(rtol=1e-5, atol=1e-5)
+    torch.testing.assert_close(q_got.cpu().float(), q_ref.float(), **tol)
+    torch.testing.assert_close(k2.cpu().float(), k1.float(), **tol)
+    torch.testing.assert_close(v2.cpu().float(), v1.float(), **tol)
+    slopes = (2.0 ** (-8.0 * torch.arange(1, H + 1) / H)).float()
+    sinks = torch.randn(H, generator=g)
+    for sl, sk in ((slopes, sinks), (None, None)):
+        ref = torch_ref.window_attention(q_ref, k1, v1, G, Dv, pt, _i32(slots, "cpu"), _i32(seq, "cpu"), _i32(q_lens, "cpu"), ps, 0.3, cap, window, sl, sk)
+        got = ops.window_attention(q_ref.to(DEV), k1.to(DEV), v1.to(DEV), G, Dv, pt.to(DEV), _i32(slots), _i32(seq), _i32(cu), _i32(q_lens), max(q_lens),
+                                   ps, 0.3, cap, window, None if sl is None else sl.to(DEV), None if sk is None else sk.to(DEV))
+        torch.testing.assert_close(got.cpu().float(), ref, **(dict(rtol=2e-2, atol=2e-2) if dtype == torch.bfloat16 else dict(rtol=2e-4, atol=2e-5)))
+    # decode form: the last token of every request alone
+    last = torch.tensor([c - 1 for c in cu[1:]])
+    qd = q_ref[last].contiguous()
+    ref = torch_ref.window_attention(qd, k1, v1, G, Dv, pt, _i32(slots, "cpu"), _i32(seq, "cpu"), None, ps, 0.3, cap, window, slopes, sinks)
+    got = ops.window_attention(qd.to(DEV), k1.to(DEV), v1.to(DEV), G, Dv, pt.to(DEV), _i32(slots), _i32(seq), None, None, 1, ps, 0.3, cap, window,
+                               slopes.to(DEV), sinks.to(DEV))
+    torch.testing.assert_close(got.cpu().float(), ref, **(dict(rtol=2e-2, atol=2e-2) if dtype == torch.bfloat16 else dict(rtol=2e-4, atol=2e-5)))
+
+
+def test_window_edge_on_the_kernel():
+    """a key whose value stands out must count as the oldest key inside the window and vanish one step later, in a portion and in decode"""
+    _need()
+    g = torch.Generator().manual_seed(4)
+    H, G, D, Dv, W, ps = 2, 1, 8, 4, 70, 16
+    pt, kc, vc = _paged(1, 400, ps, 8, torch.float32, g)
+    kc.mul_(0.05)
+    vc.mul_(0.01)
+    mark = 131
+    slot = int(pt[1, mark // ps]) * ps + mark % ps
+    kc[slot, 0, :D] = 0.0
+    kc[slot, 0, 0] = 4.0
+    vc[slot, 0, :Dv] = 100.0
+    for qpos in (mark + W - 1, mark + W):
+        for n in (1, 9):
+            q = torch.zeros(n, H, D)
+            q[-1, :, 0] = 5.0
+            args = (G, Dv, pt.to(DEV), _i32([1]), _i32([qpos + 1]))
+            got = ops.window_attention(q.to(DEV), kc.to(DEV), vc.to(DEV), *args, _i32([0, n]) if n > 1 else None, _i32([n]) if n > 1 else None, n, ps, 1.0,
+                                       0.0, W, None, torch.zeros(H, device=DEV))
+            seen = got[-1, 0, 0].item() > 50.0
+            assert seen == (qpos == mark + W - 1), (qpos, n, got[-1])
+
+
+def test_router_and_combine():
+    _need()
+    g = torch.Generator().manual_seed(5)
+    for E, n_real, K in ((16, 12, 2), (5, 5, 5), (40, 33, 6), (3, 1, 1), (300, 290, 8)):
+        logits = torch.randn(50, E + 1, generator=g)[:, :E] * 2          # a column view, like the model's
+        corr = torch.randn(E, generator=g) * 0.1
+        w1, i1, d1 = torch_ref.softmax_bias_route(logits, corr, K, n_real)
+        w2, i2, d2 = moe_ops.softmax_bias_route(logits.to(DEV), corr.to(DEV), K, n_real)
+        o1, o2 = i1.long().sort(-1), i2.cpu().long().sort(-1)
+        assert torch.equal(o1.values, o2.values)
+        torch.testing.assert_close(w2.cpu().gather(1, o2.indices), w1.gather(1, o1.indices), rtol=1e-5, atol=1e-7)
+        torch.testing.assert_close(d2.cpu(), d1, rtol=1e-5, atol=1e-7)
+    for dtype in (torch.float32, torch.bfloat16):
+        y, h, sh = (torch.randn(9, 72, generator=g).to(dtype) for _ in range(3))
+        idw, sg = torch.rand(9, generator=g), torch.randn(9, generator=g)
+        ref = moe_ops.moe_identity_shared_combine(y.clone(), h, idw, sh, sg)
+        got = moe_ops.moe_identity_shared_combine(y.clone().to(DEV), h.to(DEV), idw.to(DEV), sh.to(DEV), sg.to(DEV))
+        torch.testing.assert_close(got.cpu().float(), ref.float(), rtol=1e-2 if dtype == torch.bfloat16 else 1e-5, atol=1e-2 if dtype == torch.bfloat16 else 1e-5)
+
+
+# ------------------------------------------------------------------ the engine on CUDA against the oracle
+def _engine_case(tmp_path, dtype, cfg, seed, tol):
+    from test_zaparax import Harness, _tokens
+
+    h = Harness(tmp_path, cfg, seed=seed, device="cuda", dtype=dtype, page=16, max_tokens=1024)
+    V = cfg["vocab"]
+    a, b, c = _tokens(150, V, 1), _tokens(41, V, 2), _tokens(3, V, 3)
+    ra, rb, rc = h.oracle(a), h.oracle(b), h.oracle(c)
+    scale = float(np.abs(ra).mean()) + 1e-6
+
+    def close(x, y):
+        err = float(np.abs(x - y).max()) / scale
+        assert err < tol, err
+
+    close(h.step([("a", a, range(len(a)))], ["a"]), ra)                                            # whole
+    close(h.run_cut("a2", a, [100, 2, 17]), ra)                                                    # portions, then token by token
+    out = h.step([("a", a[:90], range(90)), ("b", b[:7], range(7)), ("c", c, range(3))], ["c"])    # unequal batch
+    close(out[:90], ra[:90]); close(out[90:97], rb[:7]); close(out[97:], rc)
+    out = h.step([("a", a[90:], range(60)), ("b", b[7:8], range(1))], ["a"])
+    close(out[:60], ra[90:]); close(out[60:], rb[7:8])
+    out = h.step([("b", b[8:], range(len(b) - 8)), ("d", c, range(3))], ["b", "d"])                # "d" reuses a freed slot and pages
+    close(out[:len(b) - 8], rb[8:]); close(out[len(b) - 8:], rc)
+    h.close()
+
+
+def test_engine_on_cuda_fp32(tmp_path):
+    _need()
+    from test_zaparax import MIXED
+
+    _engine_case(tmp_path, "float32", MIXED, 21, 2e-4)
+
+
+def test_engine_on_cuda_bf16(tmp_path):
+    _need()
+    from test_zaparax import EVERY_EXPERT
+
+    _engine_case(tmp_path, "bfloat16", EVERY_EXPERT, 22, 8e-2)
+
+
+def test_engine_on_cuda_lane_friendly_sizes_fp32(tmp_path):
+    """sizes the vectorised and tensor-core routes accept (multiples of 64), so that those routes are the ones checked"""
+    _need()
+    from test_zaparax import WIDE
+
+    _engine_case(tmp_path, "float32", WIDE, 23, 2e-4)
+
+
+def test_engine_on_cuda_lane_friendly_sizes_bf16(tmp_path):
+    _need()
+    from test_zaparax import WIDE_EVERY_EXPERT
+
+    _engine_case(tmp_path, "bfloat16", WIDE_EVERY_EXPERT, 24, 8e-2)
