@@ -47,7 +47,7 @@ def fused_moe(x: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, topk_w: torc
         out = torch.empty_like(x)
         torch.ops.sglb.moe_grouped_mlp_glu(x, w13, w2, topk_w, topk_ids, out, expert_offset, float(limit), float(alpha))
         return out
-    if act is None and x.dtype == torch.bfloat16 and _has("moe_grouped_mlp"):
+    if act is None and x.dtype == torch.bfloat16 and _has("moe_grouped_mlp") and H % 32 == 0 and I % 16 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0:
         out = torch.empty_like(x)
         torch.ops.sglb.moe_grouped_mlp(x, w13, w2, topk_w, topk_ids, out, expert_offset)
         return out
