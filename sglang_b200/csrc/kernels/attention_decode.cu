@@ -55,6 +55,7 @@ struct DecodeParams {
   const int* seq_lens;
   int pt_stride, Hq, Hkv, G, page_size, num_splits, B;
   float scale_log2, logit_cap;
+  const float* slopes;      // optional [Hq]: distance bias, score -= slopes[h] * (seq_len - 1 - key position), applied after the cap
   int window;
   int total_items;
   int* sched;             // [0] next item, [1] CTAs finished (the last one re-arms both)
@@ -265,7 +266,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     const int row = (q4 << 5) + lane;                     // key index inside the tile / output dim in the epilogue
     const uint32_t lane_addr = (uint32_t)(q4 << 5) << 16;
     const float scale_log2 = p.scale_log2;
-    const float cap = p.logit_cap, inv_cap = HAS_CAP ? 1.f / p.logit_cap : 0.f;
+    const float cap = p.logit_cap, inv_cap = (HAS_CAP && p.logit_cap > 0.f) ? 1.f / p.logit_cap : 0.f;
     const float scale_nat = scale_log2 * 0.6931471805599453f, inv_scale_nat = 1.f / scale_nat;
     uint32_t n_it = 0, n_q = 0, g = 0;
     for (;;) {
@@ -290,6 +291,9 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       const int n_tiles = it.n_tiles;
       if (lane == 0) DA_DBG(3, n_q, g);
       const int kv_first = p.window > 0 ? it.seq_len - p.window : 0;
+      float slope[GMAX];
+#pragma unroll
+      for (int i = 0; i < GMAX; ++i) slope[i] = (HAS_CAP && p.slopes && i < G) ? p.slopes[it.kvh * G + i] : 0.f;
       float m_run[GMAX], l_part[GMAX];
 #pragma unroll
       for (int i = 0; i < GMAX; ++i) { m_run[i] = -INFINITY; l_part[i] = 0.f; }
@@ -322,7 +326,11 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 #pragma unroll
         for (int i = 0; i < GMAX; ++i) {
           float x = __uint_as_float(sr[i]);
-          if (HAS_CAP) x = cap * tanhf(x * scale_nat * inv_cap) * inv_scale_nat;
+          if (HAS_CAP) {
+            float y = x * scale_nat;
+            if (cap > 0.f) y = cap * tanhf(y * inv_cap);
+            x = (y - slope[i] * (float)(it.seq_len - 1 - key)) * inv_scale_nat;
+          }
           sv[i] = live ? x * scale_log2 : -INFINITY;
           wmax[i] = warp_max(sv[i]);
         }
@@ -468,7 +476,7 @@ void attn_decode_set_prof(long long* buf) { g_da_prof = buf; }
 void attn_decode_tc(const void* q, const void* k_cache, const void* v_cache, void* out, float* lse, float* part_o, float* part_lse,
                     const int* page_table, int pt_stride, const int* req_slots, const int* seq_lens, int B, int q_stride, int Hq, int Hkv,
                     int D, int num_slots, int page_size, int num_splits, float scale, int window, float logit_cap, int* sched, int num_sms,
-                    cudaStream_t stream) {
+                    cudaStream_t stream, const float* slopes) {
   if (!attn_decode_tc_supported(Hq, Hkv, D, page_size)) throw std::runtime_error("sglb attn_decode_tc: unsupported shape");
   if (sched == nullptr) throw std::runtime_error("sglb attn_decode_tc: needs the work-queue counters");
   const int G = Hq / Hkv;
@@ -486,10 +494,10 @@ void attn_decode_tc(const void* q, const void* k_cache, const void* v_cache, voi
   p.out = (__nv_bfloat16*)out; p.part_o = part_o; p.part_lse = part_lse; p.lse = lse;
   p.page_table = page_table; p.req_slots = req_slots; p.seq_lens = seq_lens;
   p.pt_stride = pt_stride; p.Hq = Hq; p.Hkv = Hkv; p.G = G; p.page_size = page_size; p.num_splits = num_splits; p.B = B;
-  p.scale_log2 = scale * 1.4426950408889634f; p.logit_cap = logit_cap; p.window = window;
+  p.scale_log2 = scale * 1.4426950408889634f; p.logit_cap = logit_cap; p.window = window; p.slopes = slopes;
   p.total_items = B * Hkv * num_splits; p.sched = sched; p.prof = g_da_prof;
   const int ctas = std::min(p.total_items, num_sms);
-  const bool capped = logit_cap > 0.f;
+  const bool capped = logit_cap > 0.f || slopes != nullptr;
 #define SGLB_DA_LAUNCH(GM_, CAP_)                                                                                                    \
   do {                                                                                                                              \
     static bool configured = false;                                                                                                 \

@@ -45,6 +45,7 @@ struct AttnParams {
   // persistent variant: work items = the (x, y, z) cells of the classic grid, handed out by an atomic counter
   int gx, gy, total_items;
   int* sched;         // [0] next item, [1] CTAs finished (the last one resets both: graph-replay safe)
+  const float* slopes;        // optional [Hq]: distance bias, score -= slopes[h] * (query position - key position), applied after the cap
   const unsigned* tree_anc;   // speculative tree verify: [T] bit k of tree_anc[t] = query token t may see draft key `prefix + k` (classic launch)
 };
 
@@ -216,8 +217,9 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     float m_i = -INFINITY, l_i = 0.f;
     // loop-invariant uniforms hoisted into registers
     const float scale_log2 = p.scale_log2;
-    const float cap = p.logit_cap, inv_cap = HAS_CAP ? 1.f / p.logit_cap : 0.f;
+    const float cap = p.logit_cap, inv_cap = (HAS_CAP && p.logit_cap > 0.f) ? 1.f / p.logit_cap : 0.f;
     const float scale_nat = scale_log2 * 0.6931471805599453f, inv_scale_nat = 1.f / scale_nat;
+    const float slope = (HAS_CAP && p.slopes) ? p.slopes[kvh * G + (r % G)] : 0.f;      // this row's head
     const int kv_last = p.causal ? min(seq_len - 1, q_pos) : seq_len - 1;
     const int kv_first = p.window > 0 ? q_pos - p.window + 1 : -(1 << 30);
 
@@ -238,13 +240,15 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                                (p.window > 0 && kv0 < prefix + t_hi - p.window);
         // The inner loops are kept branch-free and tiny (the 128-wide body is fully unrolled: any per-element branch or
         // constant-bank reload multiplies into thousands of instructions and thrashes the instruction cache).
-        if (HAS_CAP) {   // Gemma-2 style soft-capping (separate template instance): rewrite raw so raw*scale_log2 is the capped logit
+        if (HAS_CAP) {   // soft-capping and / or distance bias (separate template instance): rewrite raw so raw*scale_log2 is the final logit
+          const float off = -slope * (float)(q_pos - kv0);      // bias of column 0; column c adds slope * c
 #pragma unroll
           for (int c = 0; c < NC; ++c)
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
               const float x = __uint_as_float(sr[c][i]) * scale_nat;
-              sr[c][i] = __float_as_uint(cap * tanhf(x * inv_cap) * inv_scale_nat);
+              const float y = cap > 0.f ? cap * tanhf(x * inv_cap) : x;
+              sr[c][i] = __float_as_uint(fmaf(slope, (float)(c * 32 + i), y + off) * inv_scale_nat);
             }
         }
         float mx_raw = -INFINITY;
@@ -585,7 +589,7 @@ attn_fwd_tc_persist_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
     const int r = (q << 5) + lane;
     const uint32_t lane_addr = (uint32_t)(q << 5) << 16;
     const float scale_log2 = p.scale_log2;
-    const float cap = p.logit_cap, inv_cap = HAS_CAP ? 1.f / p.logit_cap : 0.f;
+    const float cap = p.logit_cap, inv_cap = (HAS_CAP && p.logit_cap > 0.f) ? 1.f / p.logit_cap : 0.f;
     const float scale_nat = scale_log2 * 0.6931471805599453f, inv_scale_nat = 1.f / scale_nat;
     uint32_t n_it = 0, n_q = 0, g = 0;
     for (;;) {
@@ -615,6 +619,7 @@ attn_fwd_tc_persist_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
       const int n_tiles = it.n_tiles;
       if (lane == 0) SGLB_ATT_DBG(3, n_q, g);
       const int q_pos = it.prefix + tok;
+      const float slope = (HAS_CAP && p.slopes) ? p.slopes[it.kvh * G + (r % G)] : 0.f;
       float m_i = -INFINITY, l_i = 0.f;
       const int kv_last = p.causal ? min(it.seq_len - 1, q_pos) : it.seq_len - 1;
       const int kv_first = p.window > 0 ? q_pos - p.window + 1 : -(1 << 30);
@@ -635,12 +640,14 @@ attn_fwd_tc_persist_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
           const bool need_mask = (kv0 + KT > it.kv_hi) || (p.causal && kv0 + KT - 1 > it.prefix + it.t0) ||
                                  (p.window > 0 && kv0 < it.prefix + it.t_hi - p.window);
           if (HAS_CAP) {
+            const float off = -slope * (float)(q_pos - kv0);
 #pragma unroll
             for (int c = 0; c < NC; ++c)
 #pragma unroll
               for (int i = 0; i < 32; ++i) {
                 const float x = __uint_as_float(sr[c][i]) * scale_nat;
-                sr[c][i] = __float_as_uint(cap * tanhf(x * inv_cap) * inv_scale_nat);
+                const float y = cap > 0.f ? cap * tanhf(x * inv_cap) : x;
+                sr[c][i] = __float_as_uint(fmaf(slope, (float)(c * 32 + i), y + off) * inv_scale_nat);
               }
           }
           float mx_raw = -INFINITY;
@@ -806,7 +813,7 @@ void attn_fwd_tc(const void* q, const void* k_cache, const void* v_cache, void* 
                  float* part_lse, const int* page_table, int pt_stride, const int* req_slots, const int* seq_lens,
                  const int* cu_q, int B, int T, int q_stride, int max_q_len, int Hq, int Hkv, int D, int num_slots, int page_size,
                  int num_splits, float scale, int causal, int window, float logit_cap, int* sched, int num_sms,
-                 cudaStream_t stream, const unsigned* tree_anc) {
+                 cudaStream_t stream, const unsigned* tree_anc, const float* slopes) {
   if (D != ATT_D) throw std::runtime_error("sglb attn_tc: head_dim must be 128");
   const int G = Hq / Hkv;
   if (G < 1 || G > 128 || (128 % G) != 0) throw std::runtime_error("sglb attn_tc: GQA group must divide 128");
@@ -827,7 +834,7 @@ void attn_fwd_tc(const void* q, const void* k_cache, const void* v_cache, void* 
   p.page_table = page_table; p.req_slots = req_slots; p.seq_lens = seq_lens; p.cu_q = cu_q;
   p.pt_stride = pt_stride; p.Hq = Hq; p.Hkv = Hkv; p.G = G; p.page_size = page_size; p.num_splits = num_splits; p.T = T;
   p.scale_log2 = scale * 1.4426950408889634f; p.logit_cap = logit_cap; p.causal = causal; p.window = window;
-  p.tree_anc = tree_anc;
+  p.tree_anc = tree_anc; p.slopes = slopes;
   if (tree_anc != nullptr) {
     if (max_q_len > 32 || num_splits != 1 || window > 0) throw std::runtime_error("sglb attn_tc: tree masks cover <= 32 draft nodes, no split-KV / window");
     p.causal = 0;        // every draft key is a candidate; the ancestor bits decide
@@ -836,7 +843,7 @@ void attn_fwd_tc(const void* q, const void* k_cache, const void* v_cache, void* 
   p.gx = (int)grid.x; p.gy = (int)grid.y; p.total_items = (int)(grid.x * grid.y * grid.z); p.sched = sched;
   // decode (one query token per request) is latency-bound: small KV tiles, two CTAs per SM
   const bool small = (cu_q == nullptr) && page_size <= 64;
-  const bool capped = logit_cap > 0.f;
+  const bool capped = logit_cap > 0.f || slopes != nullptr;
 #define SGLB_ATT_LAUNCH(KT_, CAP_)                                                                                         \
   do {                                                                                                                    \
     static bool configured = false;                                                                                       \

@@ -418,6 +418,25 @@ __global__ void __launch_bounds__(256) bigram_embedding_kernel(const T* __restri
       br = bigram + (size_t)row * W;
     }
     float* o = out + (size_t)(q0 + t) * W;
+    if constexpr (sizeof(T) == 2) {
+      if (W % 8 == 0) {          // 16-byte lanes: 8 bf16 of each row in, two float4 out
+        for (int c = threadIdx.x * 8; c < W; c += 256 * 8) {
+          const U4 e = ldg128(er + c);
+          U4 g = U4{0u, 0u, 0u, 0u};
+          if (br) g = ldg128(br + c);
+          const uint32_t ew[4] = {e.x, e.y, e.z, e.w}, gw[4] = {g.x, g.y, g.z, g.w};
+          float r[8];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            r[2 * k] = bf16_lo(ew[k]) * scale + bf16_lo(gw[k]);
+            r[2 * k + 1] = bf16_hi(ew[k]) * scale + bf16_hi(gw[k]);
+          }
+          *reinterpret_cast<float4*>(o + c) = make_float4(r[0], r[1], r[2], r[3]);
+          *reinterpret_cast<float4*>(o + c + 4) = make_float4(r[4], r[5], r[6], r[7]);
+        }
+        continue;
+      }
+    }
     for (int c = threadIdx.x; c < W; c += 256) o[c] = be_ld<T>(er + c) * scale + (br ? be_ld<T>(br + c) : 0.f);
   }
 }

@@ -243,13 +243,13 @@ bool gated_delta_update(float* state, const int* req_slots, const float* u, int 
 //   dt = softplus(dt_raw + dt_bias);  S <- exp(-exp(A_log) dt) S + dt B x^T;  y = S^T C + D x;  y <- y * silu(z)       (S fp32 [N, P] per head)
 // The columns of S (one per channel p of the head) never mix, so a CTA owns (request, head, a block of PC = 128 / KS columns) and walks the
 // request's tokens in order; a column lives in the registers of KS neighbouring lanes (ROWS rows each, row = r * KS + ks) and S^T C closes
-// with log2(KS) shuffles.  Tokens are staged 16 at a time: B, C, x, dt and the decay go to shared memory, then 16 recurrence steps run out of
-// shared memory (broadcast reads).  The state is read once and written once per call; a request whose cached length is zero starts from
-// S = 0 whatever its slot holds.  Token order is fixed, so a position's output is bit-identical however the prompt was cut or batched.
+// with log2(KS) shuffles.  Tokens are staged TC at a time through two shared-memory buffers: while the recurrence runs TC steps out of one
+// buffer (broadcast reads, nothing global inside the serial chain), cp.async fills the other with the next tokens' B, C and x, and their z
+// and dt wait in registers; outputs are collected in shared memory and written out coalesced per chunk.  The state is read once and written
+// once per call; a request whose cached length is zero starts from S = 0 whatever its slot holds.  Token order is fixed, so a position's
+// output is bit-identical however the prompt was cut or batched.
 // Reference counterpart: layers/attention/mamba/ops (chunked SSD scan for prompts, selective_state_update for decode).
 namespace {
-
-constexpr int M2_TC = 16;
 
 struct Mamba2Params {
   const float* u; int ldu;                       // conv outputs [T, ldu] = [x (H*P) | B (G*N) | C (G*N)]
@@ -263,11 +263,16 @@ struct Mamba2Params {
 };
 
 __device__ __forceinline__ float m2_softplus(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+__device__ __forceinline__ void m2_cp4(float* dst, const float* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void m2_cp_wait() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
-template <typename TZ, int ROWS, int KS>
+template <typename TZ, int ROWS, int KS, int TC>
 __global__ void __launch_bounds__(128) mamba2_scan_kernel(const Mamba2Params p) {
   extern __shared__ float sm[];
   constexpr int PC = 128 / KS;
+  constexpr int ZR = (TC * PC + 127) / 128;         // z values a thread holds for the next chunk
   const int b = blockIdx.y;
   const int q0 = p.cu_q ? p.cu_q[b] : b;
   const int n = p.cu_q ? p.cu_q[b + 1] - q0 : 1;
@@ -278,11 +283,8 @@ __global__ void __launch_bounds__(128) mamba2_scan_kernel(const Mamba2Params p) 
   const int tid = threadIdx.x, col = tid / KS, ks = tid % KS;
   const int pp = pc * PC + col;
   const bool live = pp < P;
-  float* sB = sm;                      // [TC][N]
-  float* sC = sB + M2_TC * N;          // [TC][N]
-  float* sX = sC + M2_TC * N;          // [TC][PC]
-  float* sDt = sX + M2_TC * PC;        // [TC]
-  float* sDa = sDt + M2_TC;            // [TC]
+  const int stage = 2 * TC * N + 2 * TC * PC + 2 * TC;      // floats per buffer: B | C | x | z | dt | decay
+  float* sY = sm + 2 * stage;                               // [TC][PC]
   float S[ROWS];
   float* st = p.state + ((size_t)p.req_slots[b] * H + h) * N * P;
   const bool fresh = p.seq_lens[b] - n == 0;
@@ -297,27 +299,61 @@ __global__ void __launch_bounds__(128) mamba2_scan_kernel(const Mamba2Params p) 
   const TZ* zg = reinterpret_cast<const TZ*>(p.z);
   const TZ* dg = reinterpret_cast<const TZ*>(p.dt_raw);
   const int inner = H * P;
-  for (int t0 = 0; t0 < n; t0 += M2_TC) {
-    const int tc = min(M2_TC, n - t0);
+  const int pw = min(PC, P - pc * PC);                      // live columns of this CTA
+  float zr[ZR];
+  float dtr = 0.f;
+
+  auto issue = [&](int t0, float* buf) {      // start the copies of chunk [t0, t0 + TC) into buf; z and dt go to registers
+    const int tc = min(TC, n - t0);
+    float* sB = buf; float* sC = sB + TC * N; float* sX = sC + TC * N;
     for (int idx = tid; idx < tc * N; idx += 128) {
       const int tt = idx / N, i = idx - tt * N;
       const float* row = p.u + (size_t)(q0 + t0 + tt) * p.ldu + inner + g * N + i;
-      sB[tt * N + i] = row[0];
-      sC[tt * N + i] = row[p.G * N];
+      m2_cp4(sB + idx, row);
+      m2_cp4(sC + idx, row + p.G * N);
     }
     for (int idx = tid; idx < tc * PC; idx += 128) {
       const int tt = idx / PC, c = idx - tt * PC;
-      sX[idx] = pc * PC + c < P ? p.u[(size_t)(q0 + t0 + tt) * p.ldu + h * P + pc * PC + c] : 0.f;
+      if (c < pw) m2_cp4(sX + idx, p.u + (size_t)(q0 + t0 + tt) * p.ldu + h * P + pc * PC + c);
+    }
+#pragma unroll
+    for (int k = 0; k < ZR; ++k) {
+      const int idx = tid + k * 128, tt = idx / PC, c = idx - tt * PC;
+      zr[k] = (zg && tt < tc && c < pw) ? ld_f<TZ>(zg + (size_t)(q0 + t0 + tt) * p.ldz + h * P + pc * PC + c) : 0.f;
+    }
+    if (tid < tc) dtr = ld_f<TZ>(dg + (size_t)(q0 + t0 + tid) * p.lddt + h);
+  };
+  auto land = [&](int t0, float* buf) {       // finish what issue() started
+    const int tc = min(TC, n - t0);
+    float* sZ = buf + 2 * TC * N + TC * PC; float* sDt = sZ + TC * PC; float* sDa = sDt + TC;
+#pragma unroll
+    for (int k = 0; k < ZR; ++k) {
+      const int idx = tid + k * 128;
+      if (idx < TC * PC) sZ[idx] = zr[k];
     }
     if (tid < tc) {
-      const float dt = m2_softplus(ld_f<TZ>(dg + (size_t)(q0 + t0 + tid) * p.lddt + h) + dtb);
+      const float dt = m2_softplus(dtr + dtb);
       sDt[tid] = dt;
       sDa[tid] = expf(-a_exp * dt);
     }
-    __syncthreads();
+    m2_cp_wait();
+  };
+
+  issue(0, sm);
+  land(0, sm);
+  __syncthreads();
+  int cur = 0;
+  for (int t0 = 0; t0 < n; t0 += TC, cur ^= 1) {
+    const int tc = min(TC, n - t0);
+    float* buf = sm + cur * stage;
+    float* nxt = sm + (cur ^ 1) * stage;
+    const bool more = t0 + TC < n;
+    if (more) issue(t0 + TC, nxt);
+    const float* sB = buf; const float* sC = sB + TC * N; const float* sX = sC + TC * N; const float* sZ = sX + TC * PC;
+    const float* sDt = sZ + TC * PC; const float* sDa = sDt + TC;
     for (int tt = 0; tt < tc; ++tt) {
       const float dt = sDt[tt], da = sDa[tt];
-      const float xv = sX[tt * PC + col];
+      const float xv = live ? sX[tt * PC + col] : 0.f;
       const float dbx = dt * xv;
       const float* bb = sB + tt * N;
       const float* cc = sC + tt * N;
@@ -333,17 +369,22 @@ __global__ void __launch_bounds__(128) mamba2_scan_kernel(const Mamba2Params p) 
       float acc = a0 + a1;
 #pragma unroll
       for (int o = 1; o < KS; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-      if (live && ks == 0) {
-        float y = acc + dskip * xv;
-        const size_t at = (size_t)(q0 + t0 + tt);
+      if (ks == 0) sY[tt * PC + col] = acc + dskip * xv;
+    }
+    __syncthreads();                                         // sY complete, everyone is done with buf
+    for (int idx = tid; idx < tc * PC; idx += 128) {
+      const int tt = idx / PC, c = idx - tt * PC;
+      if (c < pw) {
+        float y = sY[idx];
         if (zg) {
-          const float zz = ld_f<TZ>(zg + at * p.ldz + h * P + pp);
+          const float zz = sZ[idx];
           y *= zz / (1.f + expf(-zz));
         }
-        p.out[at * inner + h * P + pp] = y;
+        p.out[(size_t)(q0 + t0 + tt) * inner + h * P + pc * PC + c] = y;
       }
     }
-    __syncthreads();
+    if (more) land(t0 + TC, nxt);
+    __syncthreads();                                         // nxt visible, sY free
   }
   if (live) {
 #pragma unroll
@@ -354,12 +395,12 @@ __global__ void __launch_bounds__(128) mamba2_scan_kernel(const Mamba2Params p) 
   }
 }
 
-template <typename TZ, int ROWS, int KS>
+template <typename TZ, int ROWS, int KS, int TC>
 void launch_m2(Mamba2Params p, int B, cudaStream_t stream) {
   constexpr int PC = 128 / KS;
   p.pchunks = (p.P + PC - 1) / PC;
-  const size_t smem = sizeof(float) * ((size_t)M2_TC * p.N * 2 + (size_t)M2_TC * PC + 2 * M2_TC);
-  auto kern = mamba2_scan_kernel<TZ, ROWS, KS>;
+  const size_t smem = sizeof(float) * (2 * ((size_t)2 * TC * p.N + 2 * TC * PC + 2 * TC) + (size_t)TC * PC);
+  auto kern = mamba2_scan_kernel<TZ, ROWS, KS, TC>;
   if (smem > 48 * 1024) SGLB_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   kern<<<dim3(p.H * p.pchunks, B), 128, smem, stream>>>(p);
   SGLB_CUDA_CHECK(cudaGetLastError());
@@ -368,13 +409,13 @@ void launch_m2(Mamba2Params p, int B, cudaStream_t stream) {
 template <typename TZ>
 void dispatch_m2(const Mamba2Params& p, int B, cudaStream_t stream) {
   const int N = p.N;
-  if (N <= 16) launch_m2<TZ, 16, 1>(p, B, stream);
-  else if (N <= 32) launch_m2<TZ, 16, 2>(p, B, stream);
-  else if (N <= 64) launch_m2<TZ, 16, 4>(p, B, stream);
-  else if (N <= 128) launch_m2<TZ, 16, 8>(p, B, stream);
-  else if (N <= 256) launch_m2<TZ, 16, 16>(p, B, stream);
-  else if (N <= 512) launch_m2<TZ, 16, 32>(p, B, stream);
-  else launch_m2<TZ, 32, 32>(p, B, stream);
+  if (N <= 16) launch_m2<TZ, 16, 1, 16>(p, B, stream);
+  else if (N <= 32) launch_m2<TZ, 16, 2, 16>(p, B, stream);
+  else if (N <= 64) launch_m2<TZ, 16, 4, 16>(p, B, stream);
+  else if (N <= 128) launch_m2<TZ, 16, 8, 16>(p, B, stream);
+  else if (N <= 256) launch_m2<TZ, 16, 16, 16>(p, B, stream);
+  else if (N <= 512) launch_m2<TZ, 16, 32, 8>(p, B, stream);
+  else launch_m2<TZ, 32, 32, 8>(p, B, stream);
 }
 
 }  // namespace

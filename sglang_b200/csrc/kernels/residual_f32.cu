@@ -132,6 +132,32 @@ __global__ void __launch_bounds__(256) grouped_rmsnorm_kernel(const float* __res
   for (int i = threadIdx.x; i < per; i += 256) stf<TO>(out + base + i, x[base + i] * rs * ldf<TO>(w + blockIdx.y * per + i));
 }
 
+// the same with one warp per (row, part): a CTA of 8 warps walks the parts of its row (many small parts: no CTA-wide barrier, 16-byte loads)
+template <typename TO>
+__global__ void __launch_bounds__(256) grouped_rmsnorm_warp_kernel(const float* __restrict__ x, const TO* __restrict__ w, TO* __restrict__ out, int C,
+                                                                   int per, int groups, float eps) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int g = warp; g < groups; g += 8) {
+    const size_t base = (size_t)blockIdx.x * C + (size_t)g * per;
+    const float4* xv = reinterpret_cast<const float4*>(x + base);
+    float ss = 0.f;
+    for (int i = lane; i < per / 4; i += 32) {
+      const float4 v = xv[i];
+      ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+    const float rs = 1.0f / sqrtf(warp_sum(ss) / (float)per + eps);
+    const TO* wr = w + (size_t)g * per;
+    for (int i = lane; i < per / 4; i += 32) {
+      const float4 v = xv[i];
+      TO* o = out + base + 4 * i;
+      stf<TO>(o, v.x * rs * ldf<TO>(wr + 4 * i));
+      stf<TO>(o + 1, v.y * rs * ldf<TO>(wr + 4 * i + 1));
+      stf<TO>(o + 2, v.z * rs * ldf<TO>(wr + 4 * i + 2));
+      stf<TO>(o + 3, v.w * rs * ldf<TO>(wr + 4 * i + 3));
+    }
+  }
+}
+
 }  // namespace
 
 void postnorm_add_rmsnorm_f32(float* residual, const void* delta, bool delta_bf16, const void* post_w, const void* w, void* out, bool out_bf16, int T,
@@ -156,6 +182,13 @@ void postnorm_add_rmsnorm_f32(float* residual, const void* delta, bool delta_bf1
 void grouped_rmsnorm(const float* x, const void* w, void* out, bool out_bf16, int T, int C, int groups, float eps, cudaStream_t stream) {
   if (T <= 0) return;
   if (groups <= 0 || C % groups || groups > 65535) throw std::runtime_error("sglb grouped_rmsnorm: the width must split into equal parts");
+  const int per = C / groups;
+  if (groups >= 4 && per % 4 == 0 && per <= 4096 && ((uintptr_t)x % 16) == 0) {
+    if (out_bf16) grouped_rmsnorm_warp_kernel<__nv_bfloat16><<<T, 256, 0, stream>>>(x, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, C, per, groups, eps);
+    else grouped_rmsnorm_warp_kernel<float><<<T, 256, 0, stream>>>(x, (const float*)w, (float*)out, C, per, groups, eps);
+    SGLB_CUDA_CHECK(cudaGetLastError());
+    return;
+  }
   dim3 g(T, groups);
   if (out_bf16) grouped_rmsnorm_kernel<__nv_bfloat16><<<g, 256, 0, stream>>>(x, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, C, C / groups, eps);
   else grouped_rmsnorm_kernel<float><<<g, 256, 0, stream>>>(x, (const float*)w, (float*)out, C, C / groups, eps);

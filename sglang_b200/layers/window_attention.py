@@ -7,7 +7,10 @@
 
 The projections are one GEMM with their biases in the epilogue; ``ops.qk_norm_cache_write`` normalises q and k, applies the query
 temperature and writes k / v rows into the paged pool; ``ops.window_attention`` (csrc/kernels/window_attention.cu) is the attention itself,
-one kernel for prompt portions and decode tokens.  Cap, bias, mask, sink and soft-max are fp32; the cache is in the model dtype.
+one kernel for prompt portions and decode tokens.  Cap, bias, mask, sink and soft-max are fp32; the cache is in the model dtype.  bf16
+models whose key and value heads are both 128 wide run the framework's tcgen05 attention kernels instead (``ops.paged_attention`` with
+``slopes``: the distance bias joins their score pass behind the cap, the sink enters through the log-sum-exp); every other size, and fp32
+serving, stays on the general kernel.
 
 The paged pool holds one flat row per token and plane (``cache_width`` columns, the widest layer's ``kv_heads * max(dim, vdim)``): a layer
 reads the first ``kv_heads * dim`` columns of the key plane as its key heads, so layers of different head counts and sizes share one pool.
@@ -40,6 +43,8 @@ def distance_slopes(heads: int, base: float = 8.0) -> torch.Tensor:
 
 
 class BiasedWindowAttention(nn.Module):
+    tc_route = True            # class-wide switch of the tcgen05 route (tests compare it with the general kernel)
+
     def __init__(self, width: int, heads: int, kv_heads: int, dim: int, vdim: int, scale: Optional[float], softcap: float, window: int, eps: float,
                  dtype, temp_coef: float = 0.0, temp_every: int = 1, qk_norm: bool = True, distance_bias: bool = True, sinks: bool = True,
                  bias: bool = True):
@@ -83,6 +88,19 @@ class BiasedWindowAttention(nn.Module):
         kc, vc = fb.kv_pool.k(cache_idx), fb.kv_pool.v(cache_idx)                  # [slots, 1, cache_width] each
         q = ops.qk_norm_cache_write(qkv, self.H, self.G, self.D, self.Dv, fb.positions, self.eps, self.temp_coef, self.temp_every, kc, vc,
                                     fb.out_cache_loc, self.qk_norm)
+        if self.tc_route and self.D == 128 and self.Dv == 128 and kc.shape[-1] == self.G * 128:
+            k4, v4 = kc.view(-1, self.G, 128), vc.view(-1, self.G, 128)
+            if ops.tc_attention_ok(q, k4, v4, fb.page_size):
+                # bf16, 128-wide heads: the framework's tcgen05 attention kernels (prompt tiles and split-KV decode) with the bias folded into
+                # their score pass; the sink enters through the log-sum-exp: o * exp(lse) / (exp(lse) + exp(sink))
+                lse = torch.empty(T, self.H, dtype=torch.float32, device=q.device) if self.sinks is not None else None
+                dec = fb.cu_q is None
+                o = ops.paged_attention(q, k4, v4, fb.page_table, fb.req_slots, fb.seq_lens, fb.cu_q, fb.q_lens, fb.max_q_len, fb.page_size, self.scale,
+                                        causal=True, window=self.window, logit_cap=self.softcap, num_splits=fb.num_splits if dec else 1,
+                                        workspace=fb.attn_workspace if dec else None, lse=lse, slopes=self.slopes)
+                if lse is not None:
+                    o = (o.float() * torch.sigmoid(lse - self.sinks[None, :]).unsqueeze(-1)).to(o.dtype)
+                return ops.linear(o.view(T, self.H * self.Dv), self.o_weight)
         o = ops.window_attention(q, kc, vc, self.G, self.Dv, fb.page_table, fb.req_slots, fb.seq_lens, fb.cu_q, fb.q_lens, fb.max_q_len, fb.page_size,
                                  self.scale, self.softcap, self.window, self.slopes, self.sinks)
         return ops.linear(o.view(T, self.H * self.Dv), self.o_weight)

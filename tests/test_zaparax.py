@@ -68,6 +68,8 @@ def _wide(top_all):
 
 
 WIDE, WIDE_EVERY_EXPERT = _wide(False), _wide(True)
+HEADS128_EVERY_EXPERT = _cfg([L(_attn(heads=4, kv_heads=2, dim=128, vdim=128, window=40, scale=0.09, softcap=30.0, every=16), _moe(experts=4, identity=2, top=6, ff=64, shared=128)),
+                              L(_mamba(heads=4, vdim=64, state=64, groups=2, conv=4, norm_groups=4), None)], width=128, vocab=192, loop=(0, 1, 2))
 
 
 class Harness:

@@ -163,6 +163,37 @@ def test_window_attention_and_cache_write(H, G, D, Dv, window, cap, dtype):
     torch.testing.assert_close(got.cpu().float(), ref, **(dict(rtol=2e-2, atol=2e-2) if dtype == torch.bfloat16 else dict(rtol=2e-4, atol=2e-5)))
 
 
+@pytest.mark.parametrize("H,G,window,cap", [(8, 2, 96, 50.0), (4, 4, 300, 0.0), (16, 1, -1, 20.0)])
+def test_tensor_core_route_against_the_general_kernel(H, G, window, cap):
+    """bf16 with 128-wide heads: the tcgen05 attention kernels with the distance bias in their score pass and the sink through the
+    log-sum-exp, prompt portions and decode, against the general fp32-math kernel on the same cache"""
+    _need()
+    g = torch.Generator().manual_seed(6)
+    ps, D = 64, 128
+    q_lens, cached = [200, 1, 2, 333], [700, 450, 0, 0]
+    cu, seq = _ragged(q_lens, cached)
+    T = sum(q_lens)
+    pt, kc, vc = _paged(4, max(seq), ps, G * D, torch.bfloat16, g)
+    kc, vc, pt = (kc * 0.5).to(DEV), vc.to(DEV), pt.to(DEV)
+    q = (torch.randn(T, H, D, generator=g)).to(torch.bfloat16).to(DEV)
+    slopes = (2.0 ** (-8.0 * torch.arange(1, H + 1) / H)).float().to(DEV)
+    sinks = torch.randn(H, generator=g).to(DEV)
+    k4, v4 = kc.view(-1, G, D), vc.view(-1, G, D)
+    assert ops.tc_attention_ok(q, k4, v4, ps)
+
+    def both(qq, cu_q, ql, mq, sl):
+        ref = ops.window_attention(qq, kc, vc, G, D, pt, _i32([1, 2, 3, 4]), _i32(sl), cu_q, ql, mq, ps, 0.09, cap, window, slopes, sinks).float()
+        lse = torch.empty(qq.shape[0], H, dtype=torch.float32, device=DEV)
+        o = ops.paged_attention(qq, k4, v4, pt, _i32([1, 2, 3, 4]), _i32(sl), cu_q, ql, mq, ps, 0.09, True, window, cap, lse=lse, slopes=slopes)
+        got = o.float() * torch.sigmoid(lse - sinks[None, :]).unsqueeze(-1)
+        torch.testing.assert_close(got, ref, rtol=3e-2, atol=3e-2)
+        assert (got - ref).abs().mean().item() < 4e-3
+
+    both(q, _i32(cu), _i32(q_lens), max(q_lens), seq)
+    last = torch.tensor([c - 1 for c in cu[1:]], device=DEV)
+    both(q[last].contiguous(), None, None, 1, seq)
+
+
 def test_window_edge_on_the_kernel():
     """a key whose value stands out must count as the oldest key inside the window and vanish one step later, in a portion and in decode"""
     _need()
@@ -259,3 +290,11 @@ def test_engine_on_cuda_lane_friendly_sizes_bf16(tmp_path):
     from test_zaparax import WIDE_EVERY_EXPERT
 
     _engine_case(tmp_path, "bfloat16", WIDE_EVERY_EXPERT, 24, 8e-2)
+
+
+def test_engine_on_cuda_tensor_core_route_bf16(tmp_path):
+    """128-wide key and value heads in bf16: the attention layers run the tcgen05 kernels (prompt and decode)"""
+    _need()
+    from test_zaparax import HEADS128_EVERY_EXPERT
+
+    _engine_case(tmp_path, "bfloat16", HEADS128_EVERY_EXPERT, 25, 8e-2)
