@@ -129,8 +129,22 @@ def _kernel_numbers(timer: _Timer, hbm_gbs: float, tflops: float) -> List[dict]:
         like = timer(lambda: ops.paged_attention(q, k4, v4, pt, slots, sl, cu, None if Q == 1 else ql, Q, ps, Dh ** -0.5, True, W, 50.0))
         keys = sum(min(i + 1, W) for i in range(S - Q, S))
         nbytes = q.numel() * 2 * 2 + B * min(S, W + Q) * Gk * Dh * 2 * 2
-        rec("window_attention", "prefill" if Q > 1 else "decode", f"B{B} S{S} q{Q} H{H} G{Gk} D{Dh} window{W} cap bias sink", ms, nbytes,
+        ph = "prefill" if Q > 1 else "decode"
+        rec("window_attention (general kernel: any head size, fp32 serving)", ph, f"B{B} S{S} q{Q} H{H} G{Gk} D{Dh} window{W} cap bias sink", ms, nbytes,
             "paged_attention (tcgen05 / split-KV decode kernel, same window and cap)", like, flops=4.0 * B * keys * H * Dh)
+        lse = torch.empty(B * Q, H, dtype=torch.float32, device=dev)
+        ns = 1 if Q > 1 else 4
+
+        def tc_route():          # what bf16 serving with 128-wide heads runs: the same tcgen05 kernels with the bias in the score pass + the sink
+            o = ops.paged_attention(q, k4, v4, pt, slots, sl, cu, None if Q == 1 else ql, Q, ps, Dh ** -0.5, True, W, 50.0, num_splits=ns, lse=lse,
+                                    slopes=slopes)
+            return (o.float() * torch.sigmoid(lse - sinks[None, :]).unsqueeze(-1)).to(o.dtype)
+
+        ms2 = timer(tc_route)
+        like2 = timer(lambda: ops.paged_attention(q, k4, v4, pt, slots, sl, cu, None if Q == 1 else ql, Q, ps, Dh ** -0.5, True, W, 50.0, num_splits=ns))
+        rec("window attention on the tcgen05 kernels (bias in the score pass, sink through the lse)", ph,
+            f"B{B} S{S} q{Q} H{H} G{Gk} D{Dh} window{W} cap bias sink splits{ns}", ms2, nbytes, "paged_attention (same kernels, no bias, no sink)", like2,
+            flops=4.0 * B * keys * H * Dh)
     # ---- q/k norm + cache write
     T = 8192
     qkv = torch.randn(T, (H + 2 * Gk) * Dh, device=dev, generator=g).to(torch.bfloat16)

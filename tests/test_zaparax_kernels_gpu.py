@@ -249,8 +249,15 @@ def _engine_case(tmp_path, dtype, cfg, seed, tol):
     scale = float(np.abs(ra).mean()) + 1e-6
 
     def close(x, y):
-        err = float(np.abs(x - y).max()) / scale
-        assert err < tol, err
+        if dtype == "float32":
+            err = float(np.abs(x - y).max()) / scale
+            assert err < tol, err
+            return
+        # bf16: per position, the root mean square over the vocabulary of the difference against that of the logits (means taken off)
+        d, r = x - y, y - y.mean(-1, keepdims=True)
+        d = d - d.mean(-1, keepdims=True)
+        err = np.sqrt((d ** 2).mean(-1)) / np.sqrt((r ** 2).mean(-1) + 1e-12)
+        assert float(err.max()) < tol and float(err.mean()) < 0.4 * tol, (float(err.max()), float(err.mean()))
 
     close(h.step([("a", a, range(len(a)))], ["a"]), ra)                                            # whole
     close(h.run_cut("a2", a, [100, 2, 17]), ra)                                                    # portions, then token by token
@@ -274,7 +281,7 @@ def test_engine_on_cuda_bf16(tmp_path):
     _need()
     from test_zaparax import EVERY_EXPERT
 
-    _engine_case(tmp_path, "bfloat16", EVERY_EXPERT, 22, 8e-2)
+    _engine_case(tmp_path, "bfloat16", EVERY_EXPERT, 22, 6e-2)
 
 
 def test_engine_on_cuda_lane_friendly_sizes_fp32(tmp_path):
@@ -289,7 +296,7 @@ def test_engine_on_cuda_lane_friendly_sizes_bf16(tmp_path):
     _need()
     from test_zaparax import WIDE_EVERY_EXPERT
 
-    _engine_case(tmp_path, "bfloat16", WIDE_EVERY_EXPERT, 24, 8e-2)
+    _engine_case(tmp_path, "bfloat16", WIDE_EVERY_EXPERT, 24, 6e-2)
 
 
 def test_engine_on_cuda_tensor_core_route_bf16(tmp_path):
@@ -297,4 +304,4 @@ def test_engine_on_cuda_tensor_core_route_bf16(tmp_path):
     _need()
     from test_zaparax import HEADS128_EVERY_EXPERT
 
-    _engine_case(tmp_path, "bfloat16", HEADS128_EVERY_EXPERT, 25, 8e-2)
+    _engine_case(tmp_path, "bfloat16", HEADS128_EVERY_EXPERT, 25, 6e-2)
