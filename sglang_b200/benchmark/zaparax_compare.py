@@ -145,6 +145,26 @@ def _kernel_numbers(timer: _Timer, hbm_gbs: float, tflops: float) -> List[dict]:
         rec("window attention on the tcgen05 kernels (bias in the score pass, sink through the lse)", ph,
             f"B{B} S{S} q{Q} H{H} G{Gk} D{Dh} window{W} cap bias sink splits{ns}", ms2, nbytes, "paged_attention (same kernels, no bias, no sink)", like2,
             flops=4.0 * B * keys * H * Dh)
+    # ---- the general kernel beside the framework's own general-shape attention (64-wide heads: neither takes the tcgen05 kernels)
+    Dh = 64
+    for B, S, Q in ((4, 2048, 2048), (64, 2048, 1)):
+        pages = B * S // ps
+        kc = torch.randn((pages + 1) * ps, 1, Gk * Dh, device=dev, generator=g).to(torch.bfloat16)
+        vc = torch.randn((pages + 1) * ps, 1, Gk * Dh, device=dev, generator=g).to(torch.bfloat16)
+        pt = (torch.arange(pages, dtype=torch.int32, device=dev) + 1).view(B, S // ps).contiguous()
+        slots = torch.arange(B, dtype=torch.int32, device=dev)
+        sl = torch.full((B,), S, dtype=torch.int32, device=dev)
+        ql = torch.full((B,), Q, dtype=torch.int32, device=dev)
+        cu = None if Q == 1 else torch.arange(0, B * Q + 1, Q, dtype=torch.int32, device=dev)
+        q = torch.randn(B * Q, H, Dh, device=dev, generator=g).to(torch.bfloat16)
+        ms = timer(lambda: ops.window_attention(q, kc, vc, Gk, Dh, pt, slots, sl, cu, None if Q == 1 else ql, Q, ps, Dh ** -0.5, 50.0, W, slopes, sinks))
+        k4, v4 = kc.view(-1, Gk, Dh), vc.view(-1, Gk, Dh)
+        like = timer(lambda: ops.paged_attention(q, k4, v4, pt, slots, sl, cu, None if Q == 1 else ql, Q, ps, Dh ** -0.5, True, W, 50.0, impl=1))
+        keys = sum(min(i + 1, W) for i in range(S - Q, S))
+        nbytes = q.numel() * 2 * 2 + B * min(S, W + Q) * Gk * Dh * 2 * 2
+        rec("window_attention (general kernel)", "prefill" if Q > 1 else "decode", f"B{B} S{S} q{Q} H{H} G{Gk} D{Dh} window{W} cap bias sink", ms, nbytes,
+            "paged_attention impl=1 (the framework's kernel for head sizes other than 128)", like, flops=4.0 * B * keys * H * Dh)
+    Dh = 128
     # ---- q/k norm + cache write
     T = 8192
     qkv = torch.randn(T, (H + 2 * Gk) * Dh, device=dev, generator=g).to(torch.bfloat16)

@@ -6,11 +6,11 @@
 //   window_attention    : s_ij = cap * tanh(q_i . k_j * scale / cap) - slope_h * (i - j), visible for 0 <= i - j < window;
 //                         p_ij = exp(s_ij) / (exp(sink_h) + sum_j' exp(s_ij')); o_i = sum_j p_ij v_j.
 //
-// window_attention mapping: one CTA per (tile of queries, chunk of the heads that share a key head, request): 16 rows = QT queries x HC heads.
-// Key tiles of 64 positions are gathered through the page table into shared memory as fp32 (keys padded to a multiple of 4 columns, rows
-// offset by 4 floats so that 16-byte reads of neighbouring keys do not collide).  A warp owns 4 rows: for the scores a lane owns 2 keys and
-// reuses each 16-byte key read for its 4 rows; probabilities go through a warp-private shared tile; for the output a lane owns CV value
-// columns and reuses each value read for its 4 rows.  The online soft-max starts from (max = sink, sum = 1), which is the sink's term.
+// window_attention mapping: one CTA per (tile of queries, chunk of the heads that share a key head, request): 32 rows = QT queries x HC heads.
+// Key tiles of 64 positions are gathered through the page table into shared memory as fp32 with 16-byte global loads where the sizes allow
+// (keys padded to a multiple of 4 columns, rows offset by 4 floats so that 16-byte reads of neighbouring keys do not collide).  A warp owns
+// 4 rows: for the scores a lane owns 2 keys and reuses each 16-byte key read for its 4 rows; probabilities go through a warp-private shared
+// tile; for the output a lane owns CV value columns and reuses each value read for its 4 rows.  The online soft-max starts from (max = sink, sum = 1), which is the sink's term.
 // The same kernel serves prompt portions (ragged over cu_q) and decode tokens (cu_q == nullptr: one query per request).  All math is fp32;
 // the cache and q are bf16 or fp32.
 #include <stdexcept>
@@ -63,7 +63,8 @@ __global__ void __launch_bounds__(128) qk_norm_cache_write_kernel(const T* __res
 }
 
 constexpr int WA_KT = 64;        // keys per tile
-constexpr int WA_ROWS = 16;      // (query, head) rows per CTA: 4 warps x 4 rows
+constexpr int WA_ROWS = 32;      // (query, head) rows per CTA: 8 warps x 4 rows
+constexpr int WA_NT = 256;       // threads per CTA
 
 struct WinAttnParams {
   const void* q; const void* kc; const void* vc; void* out;
@@ -73,10 +74,19 @@ struct WinAttnParams {
   const float* slopes; const float* sinks;
   int H, G, HG, HC, nchunks, QT, D, Dp, Dv;
   float scale, softcap; int window;
+  int vec;                                     // 16-byte gathers: head sizes, row stride and base addresses allow them
 };
 
+// 16 bytes of a cache row -> fp32 in shared memory
+__device__ __forceinline__ void wa_load16(const float* src, float* dst) { *reinterpret_cast<float4*>(dst) = *reinterpret_cast<const float4*>(src); }
+__device__ __forceinline__ void wa_load16(const __nv_bfloat16* src, float* dst) {
+  const U4 v = ldg128(src);
+  *reinterpret_cast<float4*>(dst) = make_float4(bf16_lo(v.x), bf16_hi(v.x), bf16_lo(v.y), bf16_hi(v.y));
+  *reinterpret_cast<float4*>(dst + 4) = make_float4(bf16_lo(v.z), bf16_hi(v.z), bf16_lo(v.w), bf16_hi(v.w));
+}
+
 template <typename T, int CV>
-__global__ void __launch_bounds__(128) window_attention_kernel(const WinAttnParams p) {
+__global__ void __launch_bounds__(WA_NT) window_attention_kernel(const WinAttnParams p) {
   extern __shared__ __align__(16) float smem[];
   const int b = blockIdx.z;
   const int q0 = p.cu_q ? p.cu_q[b] : b;
@@ -91,17 +101,17 @@ __global__ void __launch_bounds__(128) window_attention_kernel(const WinAttnPara
   const int nh = min(p.HC, p.HG - chunk * p.HC);        // heads of this CTA
   const int D = p.D, Dp = p.Dp, Dv = p.Dv, HC = p.HC;
   const int ldk = Dp + 4, ldv = 32 * CV;
-  float* sQ = smem;                                     // [16][Dp]
+  float* sQ = smem;                                     // [32][Dp]
   float* sK = sQ + WA_ROWS * Dp;                        // [64][Dp + 4]
   float* sV = sK + WA_KT * ldk;                         // [64][32 * CV]
-  float* sP = sV + WA_KT * ldv;                         // [16][64]
+  float* sP = sV + WA_KT * ldv;                         // [32][64]
   int* sSlot = reinterpret_cast<int*>(sP + WA_ROWS * WA_KT);   // [64]
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const T* qg = reinterpret_cast<const T*>(p.q);
   const T* kg = reinterpret_cast<const T*>(p.kc);
   const T* vg = reinterpret_cast<const T*>(p.vc);
   // ---- queries (times the score scale), zero rows where the tile has no query or head
-  for (int idx = tid; idx < WA_ROWS * Dp; idx += 128) {
+  for (int idx = tid; idx < WA_ROWS * Dp; idx += WA_NT) {
     const int r = idx / Dp, d = idx - r * Dp;
     const int qi = r / HC, hc = r - qi * HC;
     float v = 0.f;
@@ -136,15 +146,42 @@ __global__ void __launch_bounds__(128) window_attention_kernel(const WinAttnPara
       sSlot[tid] = j < khi ? pt[j / p.page_size] * p.page_size + j % p.page_size : -1;
     }
     __syncthreads();
-    for (int idx = tid; idx < WA_KT * Dp; idx += 128) {
-      const int jj = idx / Dp, d = idx - jj * Dp;
-      const int s = sSlot[jj];
-      sK[jj * ldk + d] = (s >= 0 && d < D) ? wa_ld<T>(kg + (size_t)s * p.ldc + (size_t)g * D + d) : 0.f;
-    }
-    for (int idx = tid; idx < WA_KT * ldv; idx += 128) {
-      const int jj = idx / ldv, c = idx - jj * ldv;
-      const int s = sSlot[jj];
-      sV[idx] = (s >= 0 && c < Dv) ? wa_ld<T>(vg + (size_t)s * p.ldc + (size_t)g * Dv + c) : 0.f;
+    if (p.vec) {
+      constexpr int EPV = 16 / (int)sizeof(T);          // elements per 16-byte load
+      const int ck = D / EPV, cv = Dv / EPV;
+      for (int idx = tid; idx < WA_KT * ck; idx += WA_NT) {
+        const int jj = idx / ck, ch = idx - jj * ck;
+        const int s = sSlot[jj];
+        float* dst = sK + jj * ldk + ch * EPV;
+        if (s >= 0) {
+          wa_load16(kg + (size_t)s * p.ldc + (size_t)g * D + ch * EPV, dst);
+        } else {
+#pragma unroll
+          for (int e = 0; e < EPV; ++e) dst[e] = 0.f;
+        }
+      }
+      for (int idx = tid; idx < WA_KT * cv; idx += WA_NT) {
+        const int jj = idx / cv, ch = idx - jj * cv;
+        const int s = sSlot[jj];
+        float* dst = sV + jj * ldv + ch * EPV;
+        if (s >= 0) {
+          wa_load16(vg + (size_t)s * p.ldc + (size_t)g * Dv + ch * EPV, dst);
+        } else {
+#pragma unroll
+          for (int e = 0; e < EPV; ++e) dst[e] = 0.f;
+        }
+      }
+    } else {
+      for (int idx = tid; idx < WA_KT * Dp; idx += WA_NT) {
+        const int jj = idx / Dp, d = idx - jj * Dp;
+        const int s = sSlot[jj];
+        sK[jj * ldk + d] = (s >= 0 && d < D) ? wa_ld<T>(kg + (size_t)s * p.ldc + (size_t)g * D + d) : 0.f;
+      }
+      for (int idx = tid; idx < WA_KT * ldv; idx += WA_NT) {
+        const int jj = idx / ldv, c = idx - jj * ldv;
+        const int s = sSlot[jj];
+        sV[idx] = (s >= 0 && c < Dv) ? wa_ld<T>(vg + (size_t)s * p.ldc + (size_t)g * Dv + c) : 0.f;
+      }
     }
     __syncthreads();
     // ---- scores: lane owns keys lane and lane + 32, for the warp's 4 rows
@@ -230,7 +267,7 @@ void launch_wa(const WinAttnParams& p, int B, int max_q_len, cudaStream_t stream
   auto kern = window_attention_kernel<T, CV>;
   if (smem > 48 * 1024) SGLB_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   dim3 grid((max_q_len + p.QT - 1) / p.QT, p.G * p.nchunks, B);
-  kern<<<grid, 128, smem, stream>>>(p);
+  kern<<<grid, WA_NT, smem, stream>>>(p);
   SGLB_CUDA_CHECK(cudaGetLastError());
 }
 
@@ -272,6 +309,9 @@ void window_attention(const void* q, const void* kc, const void* vc, bool bf16, 
   p.QT = std::max(1, WA_ROWS / p.HC);
   p.D = D; p.Dp = (D + 3) / 4 * 4; p.Dv = Dv;
   p.scale = scale; p.softcap = softcap; p.window = window;
+  const size_t esz = bf16 ? 2 : 4;
+  const int epv = (int)(16 / esz);
+  p.vec = (D % epv == 0 && Dv % epv == 0 && (ldc * esz) % 16 == 0 && ((uintptr_t)kc % 16) == 0 && ((uintptr_t)vc % 16) == 0) ? 1 : 0;
   if (p.G * p.nchunks > 65535) throw std::runtime_error("sglb window_attention: too many heads for one launch");
   if (bf16) dispatch_wa<__nv_bfloat16>(p, B, max_q_len, stream);
   else dispatch_wa<float>(p, B, max_q_len, stream);
