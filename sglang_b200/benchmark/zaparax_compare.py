@@ -27,7 +27,7 @@ from .hybrid_compare import _engine_numbers, _peaks, _Timer
 def _zaparax_cfg(width: int, heads: int, experts: int, top: int, eff: int, shared: int, window: int, state: int) -> dict:
     mamba = {"type": "mamba2", "mixer": {"heads": 2 * width // 64, "vdim": 64, "state": state, "groups": 8, "conv": 4, "norm_groups": 8}}
     attn = {"type": "attention", "mixer": {"heads": heads, "kv_heads": max(1, heads // 8), "dim": 128, "vdim": 128, "mask": {"size": window},
-                                           "q_temp": {"coef": 0.1, "every": 1024}, "scale": 128 ** -0.5, "softcap": 50.0}}
+                                           "q_temp": {"coef": 0.1, "every": 1024}, "scale": 128 ** -0.5, "softcap": 30.0}}
     moe = {"kind": "moe", "expert": {"ff": eff}, "router": {"experts": experts, "identity": 2, "top": top}, "shared": {"ff": shared}}
     return {"architecture": "Zaparax", "width": width, "vocab": 32000, "norm": {"eps": 1e-6},
             "embedding": {"scale": 1.0, "bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 17}},
@@ -124,9 +124,9 @@ def _kernel_numbers(timer: _Timer, hbm_gbs: float, tflops: float) -> List[dict]:
         ql = torch.full((B,), Q, dtype=torch.int32, device=dev)
         cu = None if Q == 1 else torch.arange(0, B * Q + 1, Q, dtype=torch.int32, device=dev)
         q = torch.randn(B * Q, H, Dh, device=dev, generator=g).to(torch.bfloat16)
-        ms = timer(lambda: ops.window_attention(q, kc, vc, Gk, Dh, pt, slots, sl, cu, None if Q == 1 else ql, Q, ps, Dh ** -0.5, 50.0, W, slopes, sinks))
+        ms = timer(lambda: ops.window_attention(q, kc, vc, Gk, Dh, pt, slots, sl, cu, None if Q == 1 else ql, Q, ps, Dh ** -0.5, 30.0, W, slopes, sinks))
         k4, v4 = kc.view(-1, Gk, Dh), vc.view(-1, Gk, Dh)
-        like = timer(lambda: ops.paged_attention(q, k4, v4, pt, slots, sl, cu, None if Q == 1 else ql, Q, ps, Dh ** -0.5, True, W, 50.0))
+        like = timer(lambda: ops.paged_attention(q, k4, v4, pt, slots, sl, cu, None if Q == 1 else ql, Q, ps, Dh ** -0.5, True, W, 30.0))
         keys = sum(min(i + 1, W) for i in range(S - Q, S))
         nbytes = q.numel() * 2 * 2 + B * min(S, W + Q) * Gk * Dh * 2 * 2
         ph = "prefill" if Q > 1 else "decode"
@@ -136,12 +136,12 @@ def _kernel_numbers(timer: _Timer, hbm_gbs: float, tflops: float) -> List[dict]:
         ns = 1 if Q > 1 else 4
 
         def tc_route():          # what bf16 serving with 128-wide heads runs: the same tcgen05 kernels with the bias in the score pass + the sink
-            o = ops.paged_attention(q, k4, v4, pt, slots, sl, cu, None if Q == 1 else ql, Q, ps, Dh ** -0.5, True, W, 50.0, num_splits=ns, lse=lse,
+            o = ops.paged_attention(q, k4, v4, pt, slots, sl, cu, None if Q == 1 else ql, Q, ps, Dh ** -0.5, True, W, 30.0, num_splits=ns, lse=lse,
                                     slopes=slopes)
             return (o.float() * torch.sigmoid(lse - sinks[None, :]).unsqueeze(-1)).to(o.dtype)
 
         ms2 = timer(tc_route)
-        like2 = timer(lambda: ops.paged_attention(q, k4, v4, pt, slots, sl, cu, None if Q == 1 else ql, Q, ps, Dh ** -0.5, True, W, 50.0, num_splits=ns))
+        like2 = timer(lambda: ops.paged_attention(q, k4, v4, pt, slots, sl, cu, None if Q == 1 else ql, Q, ps, Dh ** -0.5, True, W, 30.0, num_splits=ns))
         rec("window attention on the tcgen05 kernels (bias in the score pass, sink through the lse)", ph,
             f"B{B} S{S} q{Q} H{H} G{Gk} D{Dh} window{W} cap bias sink splits{ns}", ms2, nbytes, "paged_attention (same kernels, no bias, no sink)", like2,
             flops=4.0 * B * keys * H * Dh)
@@ -157,9 +157,9 @@ def _kernel_numbers(timer: _Timer, hbm_gbs: float, tflops: float) -> List[dict]:
         ql = torch.full((B,), Q, dtype=torch.int32, device=dev)
         cu = None if Q == 1 else torch.arange(0, B * Q + 1, Q, dtype=torch.int32, device=dev)
         q = torch.randn(B * Q, H, Dh, device=dev, generator=g).to(torch.bfloat16)
-        ms = timer(lambda: ops.window_attention(q, kc, vc, Gk, Dh, pt, slots, sl, cu, None if Q == 1 else ql, Q, ps, Dh ** -0.5, 50.0, W, slopes, sinks))
+        ms = timer(lambda: ops.window_attention(q, kc, vc, Gk, Dh, pt, slots, sl, cu, None if Q == 1 else ql, Q, ps, Dh ** -0.5, 30.0, W, slopes, sinks))
         k4, v4 = kc.view(-1, Gk, Dh), vc.view(-1, Gk, Dh)
-        like = timer(lambda: ops.paged_attention(q, k4, v4, pt, slots, sl, cu, None if Q == 1 else ql, Q, ps, Dh ** -0.5, True, W, 50.0, impl=1))
+        like = timer(lambda: ops.paged_attention(q, k4, v4, pt, slots, sl, cu, None if Q == 1 else ql, Q, ps, Dh ** -0.5, True, W, 30.0, impl=1))
         keys = sum(min(i + 1, W) for i in range(S - Q, S))
         nbytes = q.numel() * 2 * 2 + B * min(S, W + Q) * Gk * Dh * 2 * 2
         rec("window_attention (general kernel)", "prefill" if Q > 1 else "decode", f"B{B} S{S} q{Q} H{H} G{Gk} D{Dh} window{W} cap bias sink", ms, nbytes,

@@ -242,8 +242,9 @@ bool gated_delta_update(float* state, const int* req_slots, const float* u, int 
 // ---------------------------------------------------------------- Mamba-2 recurrence over a ragged batch (prompt portions and decode tokens alike)
 //   dt = softplus(dt_raw + dt_bias);  S <- exp(-exp(A_log) dt) S + dt B x^T;  y = S^T C + D x;  y <- y * silu(z)       (S fp32 [N, P] per head)
 // The columns of S (one per channel p of the head) never mix, so a CTA owns (request, head, a block of PC = 128 / KS columns) and walks the
-// request's tokens in order; a column lives in the registers of KS neighbouring lanes (ROWS rows each, row = r * KS + ks) and S^T C closes
-// with log2(KS) shuffles.  Tokens are staged TC at a time through two shared-memory buffers: while the recurrence runs TC steps out of one
+// request's tokens in order; a column lives in the registers of KS neighbouring lanes (ROWS consecutive rows each, row = ks * ROWS + r) and
+// S^T C closes with log2(KS) shuffles.  B and C sit in shared memory in pieces of ROWS + 4 floats per lane slice, so that every lane reads its
+// rows with 16-byte loads and the KS slices of a warp do not collide.  Tokens are staged TC at a time through two shared-memory buffers: while the recurrence runs TC steps out of one
 // buffer (broadcast reads, nothing global inside the serial chain), cp.async fills the other with the next tokens' B, C and x, and their z
 // and dt wait in registers; outputs are collected in shared memory and written out coalesced per chunk.  The state is read once and written
 // once per call; a request whose cached length is zero starts from S = 0 whatever its slot holds.  Token order is fixed, so a position's
@@ -268,10 +269,11 @@ __device__ __forceinline__ void m2_cp4(float* dst, const float* src) {
 }
 __device__ __forceinline__ void m2_cp_wait() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
-template <typename TZ, int ROWS, int KS, int TC>
+template <typename TZ, int ROWS, int KS, int TC, int CPT>
 __global__ void __launch_bounds__(128) mamba2_scan_kernel(const Mamba2Params p) {
   extern __shared__ float sm[];
-  constexpr int PC = 128 / KS;
+  constexpr int PCH = 128 / KS;                     // columns one pass of the CTA's threads covers
+  constexpr int PC = CPT * PCH;                     // columns of the CTA: a thread owns CPT of them, PCH apart, and reuses every B / C read for all
   constexpr int ZR = (TC * PC + 127) / 128;         // z values a thread holds for the next chunk
   const int b = blockIdx.y;
   const int q0 = p.cu_q ? p.cu_q[b] : b;
@@ -281,17 +283,30 @@ __global__ void __launch_bounds__(128) mamba2_scan_kernel(const Mamba2Params p) 
   const int H = p.H, P = p.P, N = p.N;
   const int g = h / (H / p.G);
   const int tid = threadIdx.x, col = tid / KS, ks = tid % KS;
-  const int pp = pc * PC + col;
-  const bool live = pp < P;
-  const int stage = 2 * TC * N + 2 * TC * PC + 2 * TC;      // floats per buffer: B | C | x | z | dt | decay
+  int pp[CPT];
+  bool live[CPT];
+#pragma unroll
+  for (int c = 0; c < CPT; ++c) {
+    pp[c] = pc * PC + c * PCH + col;
+    live[c] = pp[c] < P;
+  }
+  constexpr int RP = ROWS + 4;                              // padded length of a lane slice of B / C
+  constexpr int NS = KS * RP;                               // floats per token of B (and of C) in shared memory
+  constexpr int stage = 2 * TC * NS + 2 * TC * PC + 2 * TC; // floats per buffer: B | C | x | z | dt | decay
   float* sY = sm + 2 * stage;                               // [TC][PC]
-  float S[ROWS];
+  float S[CPT][ROWS];
   float* st = p.state + ((size_t)p.req_slots[b] * H + h) * N * P;
   const bool fresh = p.seq_lens[b] - n == 0;
 #pragma unroll
-  for (int r = 0; r < ROWS; ++r) {
-    const int i = r * KS + ks;
-    S[r] = (live && !fresh && i < N) ? st[(size_t)i * P + pp] : 0.f;
+  for (int c = 0; c < CPT; ++c)
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+      const int i = ks * ROWS + r;
+      S[c][r] = (live[c] && !fresh && i < N) ? st[(size_t)i * P + pp[c]] : 0.f;
+    }
+  if (N < KS * ROWS) {                 // rows beyond N stay zero in both buffers (the copies never touch them)
+    for (int idx = tid; idx < 2 * stage; idx += 128) sm[idx] = 0.f;
+    __syncthreads();
   }
   const float a_exp = expf(p.A_log[h]);
   const float dskip = p.D ? p.D[h] : 0.f;
@@ -305,12 +320,13 @@ __global__ void __launch_bounds__(128) mamba2_scan_kernel(const Mamba2Params p) 
 
   auto issue = [&](int t0, float* buf) {      // start the copies of chunk [t0, t0 + TC) into buf; z and dt go to registers
     const int tc = min(TC, n - t0);
-    float* sB = buf; float* sC = sB + TC * N; float* sX = sC + TC * N;
+    float* sB = buf; float* sC = sB + TC * NS; float* sX = sC + TC * NS;
     for (int idx = tid; idx < tc * N; idx += 128) {
       const int tt = idx / N, i = idx - tt * N;
       const float* row = p.u + (size_t)(q0 + t0 + tt) * p.ldu + inner + g * N + i;
-      m2_cp4(sB + idx, row);
-      m2_cp4(sC + idx, row + p.G * N);
+      const int at = tt * NS + (i / ROWS) * RP + (i % ROWS);
+      m2_cp4(sB + at, row);
+      m2_cp4(sC + at, row + p.G * N);
     }
     for (int idx = tid; idx < tc * PC; idx += 128) {
       const int tt = idx / PC, c = idx - tt * PC;
@@ -325,7 +341,7 @@ __global__ void __launch_bounds__(128) mamba2_scan_kernel(const Mamba2Params p) 
   };
   auto land = [&](int t0, float* buf) {       // finish what issue() started
     const int tc = min(TC, n - t0);
-    float* sZ = buf + 2 * TC * N + TC * PC; float* sDt = sZ + TC * PC; float* sDa = sDt + TC;
+    float* sZ = buf + 2 * TC * NS + TC * PC; float* sDt = sZ + TC * PC; float* sDa = sDt + TC;
 #pragma unroll
     for (int k = 0; k < ZR; ++k) {
       const int idx = tid + k * 128;
@@ -349,27 +365,41 @@ __global__ void __launch_bounds__(128) mamba2_scan_kernel(const Mamba2Params p) 
     float* nxt = sm + (cur ^ 1) * stage;
     const bool more = t0 + TC < n;
     if (more) issue(t0 + TC, nxt);
-    const float* sB = buf; const float* sC = sB + TC * N; const float* sX = sC + TC * N; const float* sZ = sX + TC * PC;
+    const float* sB = buf; const float* sC = sB + TC * NS; const float* sX = sC + TC * NS; const float* sZ = sX + TC * PC;
     const float* sDt = sZ + TC * PC; const float* sDa = sDt + TC;
     for (int tt = 0; tt < tc; ++tt) {
       const float dt = sDt[tt], da = sDa[tt];
-      const float xv = live ? sX[tt * PC + col] : 0.f;
-      const float dbx = dt * xv;
-      const float* bb = sB + tt * N;
-      const float* cc = sC + tt * N;
-      float a0 = 0.f, a1 = 0.f;
+      float xv[CPT], dbx[CPT], a0[CPT], a1[CPT];
 #pragma unroll
-      for (int r = 0; r < ROWS; ++r) {
-        const int i = r * KS + ks;
-        if (i < N) {
-          S[r] = S[r] * da + dbx * bb[i];
-          if (r & 1) a1 += S[r] * cc[i]; else a0 += S[r] * cc[i];
+      for (int c = 0; c < CPT; ++c) {
+        xv[c] = live[c] ? sX[tt * PC + c * PCH + col] : 0.f;
+        dbx[c] = dt * xv[c];
+        a0[c] = a1[c] = 0.f;
+      }
+      const float4* bb = reinterpret_cast<const float4*>(sB + tt * NS + ks * RP);
+      const float4* cc = reinterpret_cast<const float4*>(sC + tt * NS + ks * RP);
+#pragma unroll
+      for (int r = 0; r < ROWS; r += 4) {
+        const float4 bv = bb[r >> 2], cv = cc[r >> 2];
+#pragma unroll
+        for (int c = 0; c < CPT; ++c) {
+          S[c][r] = S[c][r] * da + dbx[c] * bv.x;
+          S[c][r + 1] = S[c][r + 1] * da + dbx[c] * bv.y;
+          S[c][r + 2] = S[c][r + 2] * da + dbx[c] * bv.z;
+          S[c][r + 3] = S[c][r + 3] * da + dbx[c] * bv.w;
+          a0[c] += S[c][r] * cv.x;
+          a1[c] += S[c][r + 1] * cv.y;
+          a0[c] += S[c][r + 2] * cv.z;
+          a1[c] += S[c][r + 3] * cv.w;
         }
       }
-      float acc = a0 + a1;
 #pragma unroll
-      for (int o = 1; o < KS; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-      if (ks == 0) sY[tt * PC + col] = acc + dskip * xv;
+      for (int c = 0; c < CPT; ++c) {
+        float acc = a0[c] + a1[c];
+#pragma unroll
+        for (int o = 1; o < KS; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        if (ks == 0) sY[tt * PC + c * PCH + col] = acc + dskip * xv[c];
+      }
     }
     __syncthreads();                                         // sY complete, everyone is done with buf
     for (int idx = tid; idx < tc * PC; idx += 128) {
@@ -386,24 +416,36 @@ __global__ void __launch_bounds__(128) mamba2_scan_kernel(const Mamba2Params p) 
     if (more) land(t0 + TC, nxt);
     __syncthreads();                                         // nxt visible, sY free
   }
-  if (live) {
+#pragma unroll
+  for (int c = 0; c < CPT; ++c) {
+    if (!live[c]) continue;
 #pragma unroll
     for (int r = 0; r < ROWS; ++r) {
-      const int i = r * KS + ks;
-      if (i < N) st[(size_t)i * P + pp] = S[r];
+      const int i = ks * ROWS + r;
+      if (i < N) st[(size_t)i * P + pp[c]] = S[c][r];
     }
   }
 }
 
-template <typename TZ, int ROWS, int KS, int TC>
-void launch_m2(Mamba2Params p, int B, cudaStream_t stream) {
-  constexpr int PC = 128 / KS;
+template <typename TZ, int ROWS, int KS, int TC, int CPT>
+void launch_m2c(Mamba2Params p, int B, cudaStream_t stream) {
+  constexpr int PC = CPT * (128 / KS);
   p.pchunks = (p.P + PC - 1) / PC;
-  const size_t smem = sizeof(float) * (2 * ((size_t)2 * TC * p.N + 2 * TC * PC + 2 * TC) + (size_t)TC * PC);
-  auto kern = mamba2_scan_kernel<TZ, ROWS, KS, TC>;
+  const size_t smem = sizeof(float) * (2 * ((size_t)2 * TC * KS * (ROWS + 4) + 2 * TC * PC + 2 * TC) + (size_t)TC * PC);
+  auto kern = mamba2_scan_kernel<TZ, ROWS, KS, TC, CPT>;
   if (smem > 48 * 1024) SGLB_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   kern<<<dim3(p.H * p.pchunks, B), 128, smem, stream>>>(p);
   SGLB_CUDA_CHECK(cudaGetLastError());
+}
+
+// two columns per thread halve the staging and the shared-memory reads per column; taken when the head is wide enough and the grid still
+// fills the GPU about twice over
+template <typename TZ, int ROWS, int KS, int TC>
+void launch_m2(const Mamba2Params& p, int B, cudaStream_t stream) {
+  constexpr int PC2 = 2 * (128 / KS);
+  const long long ctas2 = (long long)p.H * ((p.P + PC2 - 1) / PC2) * B;
+  if (ROWS <= 16 && p.P >= PC2 && ctas2 >= 256) launch_m2c<TZ, ROWS, KS, TC, 2>(p, B, stream);
+  else launch_m2c<TZ, ROWS, KS, TC, 1>(p, B, stream);
 }
 
 template <typename TZ>

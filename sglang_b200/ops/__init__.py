@@ -533,7 +533,7 @@ def bigram_embedding(embed: torch.Tensor, bigram: Optional[torch.Tensor], ids: t
                      req_slots: torch.Tensor, seq_lens: torch.Tensor, max_q_len: int, scale: float, mul_prev: int = 0, mul_cur: int = 0,
                      buckets: int = 0) -> torch.Tensor:
     """token embedding times ``scale`` plus a hashed (previous token, token) row, straight into the fp32 residual stream
-    (csrc/kernels/elementwise.cu; contract in ``torch_ref.bigram_embedding``).  ``prev_tokens`` int32 [slots] carries every request's last
+    (csrc/kernels/elementwise.cu; semantics in ``torch_ref.bigram_embedding``).  ``prev_tokens`` int32 [slots] carries every request's last
     token from call to call."""
     if _use_native(embed) and embed.dtype in (torch.bfloat16, torch.float32) and embed.is_contiguous() and ids.dtype == torch.int32 \
             and req_slots.numel() <= 65535 and (bigram is None or (bigram.dtype == embed.dtype and bigram.is_contiguous())):
@@ -558,7 +558,7 @@ def mamba2_scan(u: torch.Tensor, z: Optional[torch.Tensor], dt_raw: torch.Tensor
                 state: torch.Tensor, req_slots: torch.Tensor, seq_lens: torch.Tensor, cu_q: Optional[torch.Tensor], q_lens: Optional[torch.Tensor],
                 H: int, P: int, N: int, G: int) -> torch.Tensor:
     """Mamba-2 recurrence over a ragged batch (prompt portions and single decode tokens alike): softplus step size, decay, the fp32 state update
-    and read-out, the skip term and the silu(z) gate in one kernel (csrc/kernels/mamba.cu; contract in ``torch_ref.mamba2_scan``).  ``z`` and
+    and read-out, the skip term and the silu(z) gate in one kernel (csrc/kernels/mamba.cu; semantics in ``torch_ref.mamba2_scan``).  ``z`` and
     ``dt_raw`` may be column views of the projection's output."""
     if (_use_native(u) and u.dtype == torch.float32 and u.is_contiguous() and state.dtype == torch.float32 and N <= 1024 and req_slots.numel() <= 65535
             and dt_raw.stride(1) == 1 and dt_raw.dtype in (torch.bfloat16, torch.float32) and (z is None or (z.stride(1) == 1 and z.dtype == dt_raw.dtype))):
@@ -572,7 +572,7 @@ def mamba2_scan(u: torch.Tensor, z: Optional[torch.Tensor], dt_raw: torch.Tensor
 def qk_norm_cache_write(qkv: torch.Tensor, H: int, G: int, D: int, Dv: int, positions: torch.Tensor, eps: float, temp_coef: float, temp_every: int,
                         k_cache: torch.Tensor, v_cache: torch.Tensor, out_cache_loc: torch.Tensor, normalise: bool = True) -> torch.Tensor:
     """per-head unit-RMS q and k, position-dependent query temperature, and the write of k / v rows into the paged cache, one kernel
-    (csrc/kernels/window_attention.cu; contract in ``torch_ref.qk_norm_cache_write``).  Returns q [T, H, D] in the cache dtype."""
+    (csrc/kernels/window_attention.cu; semantics in ``torch_ref.qk_norm_cache_write``).  Returns q [T, H, D] in the cache dtype."""
     if (_use_native(qkv) and qkv.dtype in (torch.bfloat16, torch.float32) and qkv.is_contiguous() and k_cache.dtype == qkv.dtype and v_cache.dtype == qkv.dtype
             and k_cache.stride(-1) == 1 and v_cache.stride(-1) == 1 and k_cache.stride(0) == v_cache.stride(0)):
         q = torch.empty(qkv.shape[0], H, D, dtype=qkv.dtype, device=qkv.device)
@@ -586,7 +586,7 @@ def window_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
                      seq_lens: torch.Tensor, cu_q: Optional[torch.Tensor], q_lens: Optional[torch.Tensor], max_q_len: int, page_size: int, scale: float,
                      softcap: float = 0.0, window: int = -1, slopes: Optional[torch.Tensor] = None, sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
     """paged grouped-query attention with a tanh score cap, a per-head distance bias, a sliding window and soft-max sinks, for prompt portions
-    and decode tokens (csrc/kernels/window_attention.cu; contract in ``torch_ref.window_attention``).  Returns [T, H, Dv] in q's dtype."""
+    and decode tokens (csrc/kernels/window_attention.cu; semantics in ``torch_ref.window_attention``).  Returns [T, H, Dv] in q's dtype."""
     T, H, D = q.shape
     if (_use_native(q) and q.dtype in (torch.bfloat16, torch.float32) and q.is_contiguous() and k_cache.dtype == q.dtype and v_cache.dtype == q.dtype
             and D <= 256 and Dv <= 256 and req_slots.numel() <= 65535 and k_cache.stride(0) == v_cache.stride(0)):

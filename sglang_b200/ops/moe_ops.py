@@ -47,7 +47,7 @@ def fused_moe(x: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, topk_w: torc
         out = torch.empty_like(x)
         torch.ops.sglb.moe_grouped_mlp_glu(x, w13, w2, topk_w, topk_ids, out, expert_offset, float(limit), float(alpha))
         return out
-    if act is None and x.dtype == torch.bfloat16 and _has("moe_grouped_mlp") and H % 32 == 0 and I % 16 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0:
+    if act is None and x.dtype == torch.bfloat16 and _has("moe_grouped_mlp") and H % 32 == 0 and I % 32 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0:
         out = torch.empty_like(x)
         torch.ops.sglb.moe_grouped_mlp(x, w13, w2, topk_w, topk_ids, out, expert_offset)
         return out
@@ -82,7 +82,7 @@ def _fused_moe_sorted(x, w13, w2, topk_w, topk_ids, expert_offset, act=None):
 
 def softmax_bias_route(logits: torch.Tensor, correction, top_k: int, n_real: int):
     """soft-max scores over real and identity experts, choice by ``score + correction``, weights = the chosen plain scores (warp-per-token
-    kernel in csrc/kernels/moe.cu; contract in ``torch_ref.softmax_bias_route``) -> (weights, ids, summed weight of the identity picks)"""
+    kernel in csrc/kernels/moe.cu; semantics in ``torch_ref.softmax_bias_route``) -> (weights, ids, summed weight of the identity picks)"""
     T, E = logits.shape
     if logits.is_cuda and _has("moe_softmax_bias_route") and logits.dtype == torch.float32 and logits.stride(1) == 1 and E <= 1024 and top_k <= 32:
         w = torch.empty(T, top_k, dtype=torch.float32, device=logits.device)

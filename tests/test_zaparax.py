@@ -72,6 +72,41 @@ HEADS128_EVERY_EXPERT = _cfg([L(_attn(heads=4, kv_heads=2, dim=128, vdim=128, wi
                               L(_mamba(heads=4, vdim=64, state=64, groups=2, conv=4, norm_groups=4), None)], width=128, vocab=192, loop=(0, 1, 2))
 
 
+def drawn_config(seed, every_expert=False, friendly=False):
+    """a randomly drawn stack: order of layers, head counts and sizes, state sizes, taps, windows from 1 to beyond the prompt, expert counts,
+    identity and shared experts, loop bounds and passes, bigram constants.  ``friendly``: sizes in multiples of 16 (vector lanes, GEMM tiles)"""
+    rng = np.random.default_rng(seed)
+    pick = lambda *a: a[int(rng.integers(len(a)))]
+    u = 16 if friendly else 1
+    layers = []
+    for _ in range(int(rng.integers(2, 6))):
+        if rng.random() < 0.5:
+            g = pick(1, 2, 3)
+            h = g * pick(1, 2, 4)
+            vd = pick(8, 16, 32) if friendly else pick(3, 4, 7, 10)
+            ng = pick(*[k for k in (1, 2, 3, 4, 6) if (h * vd) % k == 0])
+            mix = _mamba(heads=h, vdim=vd, state=pick(16, 32) if friendly else pick(2, 5, 9, 17, 33), groups=g, conv=pick(1, 2, 3, 4, 5), norm_groups=ng)
+        else:
+            g = pick(1, 2, 3)
+            mix = _attn(heads=g * pick(1, 2, 3, 5), kv_heads=g, dim=pick(16, 32) if friendly else pick(2, 5, 8, 12), vdim=pick(16, 48) if friendly else pick(3, 6, 9),
+                        window=pick(0, 1, 2, 5, 16, 33, 200), scale=pick(0.3, 0.7, 1.1), softcap=pick(0.0, 2.0, 6.0), coef=pick(0.0, 0.3), every=pick(1, 4, 9))
+        if rng.random() < 0.25:
+            layers.append(L(mix, None))
+            continue
+        E, n_id = pick(1, 2, 4, 7), pick(0, 1, 3)
+        top = E + n_id if every_expert else int(rng.integers(1, E + n_id + 1))
+        layers.append(L(mix, _moe(experts=E, identity=n_id, top=top, ff=pick(16, 32) if friendly else pick(3, 8, 11), shared=pick(0, 16 if friendly else 5, 32 if friendly else 12))))
+    n = len(layers)
+    a = int(rng.integers(0, n))
+    b = int(rng.integers(a + 1, n + 1))
+    loop = pick(None, (a, b, pick(1, 2, 3)))
+    c = _cfg(layers, width=pick(32, 64) if friendly else pick(10, 24, 36), vocab=pick(64, 128) if friendly else pick(19, 50, 131), loop=loop,
+             bigram=rng.random() < 0.7, scale=pick(1.0, 2.5, 8.0))
+    if "bigram" in c["embedding"]:
+        c["embedding"]["bigram"] = {"buckets": pick(5, 37, 101), "mul_prev": pick(1, 11, 1000003), "mul_cur": pick(1, 5, 77)}
+    return c
+
+
 class Harness:
     """a model folder with random weights, an engine on it, and the oracle's logits for any token sequence"""
 
@@ -398,3 +433,18 @@ def test_text_prompts_on_a_weights_only_folder(tmp_path):
     out = eng.generate("hello there", {"max_new_tokens": 4, "temperature": 0.7, "top_k": 5, "ignore_eos": True})
     assert len(out["output_ids"]) == 4 and isinstance(out["text"], str)
     eng.shutdown()
+
+
+@pytest.mark.parametrize("seed", [1, 2, 3])
+def test_randomly_drawn_stacks(tmp_path, seed):
+    cfg = drawn_config(seed)
+    h = Harness(tmp_path, cfg, seed=50 + seed, max_tokens=30 * PAGE)
+    V = cfg["vocab"]
+    a, b = _tokens(45, V, 1), _tokens(14, V, 2)
+    ra, rb = h.oracle(a), h.oracle(b)
+    _close(h.step([("w", a, range(len(a)))], ["w"]), ra, 3e-4)
+    _close(h.run_cut("c", a, [19, 2, 9, 2]), ra, 3e-4)
+    out = h.step([("a", a[:30], range(30)), ("b", b, range(len(b)))], ["b"])
+    _close(out[:30], ra[:30], 3e-4); _close(out[30:], rb, 3e-4)
+    _close(h.step([("a", a[30:], range(15))], ["a"]), ra[30:], 3e-4)
+    h.close()

@@ -78,7 +78,7 @@ def test_sandwich_norm_and_grouped_norm(dtype, W):
         torch.testing.assert_close(got.cpu().float(), ref.float(), rtol=1e-2 if dtype == torch.bfloat16 else 1e-5, atol=1e-2 if dtype == torch.bfloat16 else 1e-5)
 
 
-@pytest.mark.parametrize("H,P,N,G", [(8, 32, 32, 2), (3, 5, 7, 1), (4, 64, 128, 4), (2, 130, 16, 2), (6, 24, 200, 3), (1, 8, 600, 1)])
+@pytest.mark.parametrize("H,P,N,G", [(8, 16, 32, 4), (3, 5, 7, 1), (4, 64, 128, 4), (2, 130, 16, 2), (6, 24, 200, 3), (1, 8, 600, 1)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_mamba2_scan(H, P, N, G, dtype):
     _need()
@@ -122,8 +122,9 @@ def _paged(n_req, max_len, ps, width, dtype, g):
     return pt, kc, vc
 
 
-@pytest.mark.parametrize("H,G,D,Dv,window,cap", [(8, 1, 64, 64, 96, 50.0), (6, 2, 10, 7, 5, 3.0), (4, 4, 32, 48, -1, 0.0), (32, 1, 16, 16, 33, 20.0),
-                                                 (3, 3, 128, 128, 70, 10.0), (2, 1, 200, 256, 17, 0.0)])
+@pytest.mark.parametrize("H,G,D,Dv,window,cap", [(8, 2, 64, 64, 100, 40.0), (6, 2, 10, 7, 5, 3.0), (4, 4, 32, 48, -1, 0.0), (32, 1, 16, 16, 33, 20.0),
+                                                 (3, 3, 128, 128, 70, 10.0), (2, 1, 200, 256, 17, 0.0), (40, 1, 8, 8, 9, 0.0), (10, 2, 12, 20, 50, 5.0),
+                                                 (7, 1, 24, 40, 3, 2.0)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_window_attention_and_cache_write(H, G, D, Dv, window, cap, dtype):
     _need()
@@ -163,7 +164,7 @@ def test_window_attention_and_cache_write(H, G, D, Dv, window, cap, dtype):
     torch.testing.assert_close(got.cpu().float(), ref, **(dict(rtol=2e-2, atol=2e-2) if dtype == torch.bfloat16 else dict(rtol=2e-4, atol=2e-5)))
 
 
-@pytest.mark.parametrize("H,G,window,cap", [(8, 2, 96, 50.0), (4, 4, 300, 0.0), (16, 1, -1, 20.0)])
+@pytest.mark.parametrize("H,G,window,cap", [(8, 2, 90, 45.0), (4, 4, 300, 0.0), (16, 1, -1, 20.0)])
 def test_tensor_core_route_against_the_general_kernel(H, G, window, cap):
     """bf16 with 128-wide heads: the tcgen05 attention kernels with the distance bias in their score pass and the sink through the
     log-sum-exp, prompt portions and decode, against the general fp32-math kernel on the same cache"""
@@ -267,6 +268,14 @@ def _engine_case(tmp_path, dtype, cfg, seed, tol):
     close(out[:60], ra[90:]); close(out[60:], rb[7:8])
     out = h.step([("b", b[8:], range(len(b) - 8)), ("d", c, range(3))], ["b", "d"])                # "d" reuses a freed slot and pages
     close(out[:len(b) - 8], rb[8:]); close(out[len(b) - 8:], rc)
+    if dtype == "float32":          # greedy generation through the engine's own entry point, scheduler and sampler
+        prompts = [b[:9], c]
+        outs = h.eng.generate(input_ids=prompts, sampling_params={"max_new_tokens": 6, "temperature": 0, "ignore_eos": True})
+        for pr, o in zip(prompts, outs):
+            seq = list(pr)
+            for _ in range(6):
+                seq.append(int(h.oracle(seq)[-1].argmax()))
+            assert o["output_ids"] == seq[len(pr):]
     h.close()
 
 
@@ -305,3 +314,21 @@ def test_engine_on_cuda_tensor_core_route_bf16(tmp_path):
     from test_zaparax import HEADS128_EVERY_EXPERT
 
     _engine_case(tmp_path, "bfloat16", HEADS128_EVERY_EXPERT, 25, 6e-2)
+
+
+@pytest.mark.parametrize("seed", [11, 12, 13, 14])
+def test_engine_on_cuda_randomly_drawn_stacks_fp32(tmp_path, seed):
+    _need()
+    from test_zaparax import drawn_config
+
+    _engine_case(tmp_path, "float32", drawn_config(seed, friendly=seed % 2 == 0), 60 + seed, 3e-4)
+
+
+@pytest.mark.parametrize("seed", [21, 22])
+def test_engine_on_cuda_randomly_drawn_stacks_bf16(tmp_path, seed):
+    _need()
+    from test_zaparax import drawn_config
+
+    # small random stacks are badly conditioned in bf16 (RMS norms over a handful of numbers amplify the rounding of their inputs; the
+    # reference ops show the same error), so this run only has to stay near the oracle; the sharp comparisons are the fp32 ones
+    _engine_case(tmp_path, "bfloat16", drawn_config(seed, every_expert=True, friendly=True), 70 + seed, 0.3)
