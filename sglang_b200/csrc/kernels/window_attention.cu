@@ -28,6 +28,9 @@ template <typename T> __device__ __forceinline__ void wa_st(T* p, float v);
 template <> __device__ __forceinline__ void wa_st<float>(float* p, float v) { *p = v; }
 template <> __device__ __forceinline__ void wa_st<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16(v); }
 
+// fp32 serving takes the accurate exponential; bf16 caches the fast one (its error is far below a bf16 rounding)
+template <typename T> __device__ __forceinline__ float wa_exp(float x) { return sizeof(T) == 4 ? expf(x) : __expf(x); }
+
 template <typename T>
 __global__ void __launch_bounds__(128) qk_norm_cache_write_kernel(const T* __restrict__ qkv, int ld, int H, int G, int D, int Dv,
                                                                   const int* __restrict__ positions, float eps, float coef, int every,
@@ -218,9 +221,9 @@ __global__ void __launch_bounds__(WA_NT) window_attention_kernel(const WinAttnPa
       }
       const float mt = warp_max(fmaxf(s[0], s[1]));
       const float mn = fmaxf(m[r], mt);
-      const float corr = (m[r] == -INFINITY) ? 0.f : __expf(m[r] - mn);
-      const float p0 = (s[0] == -INFINITY) ? 0.f : __expf(s[0] - mn);
-      const float p1 = (s[1] == -INFINITY) ? 0.f : __expf(s[1] - mn);
+      const float corr = (m[r] == -INFINITY) ? 0.f : wa_exp<T>(m[r] - mn);
+      const float p0 = (s[0] == -INFINITY) ? 0.f : wa_exp<T>(s[0] - mn);
+      const float p1 = (s[1] == -INFINITY) ? 0.f : wa_exp<T>(s[1] - mn);
       l[r] = l[r] * corr + warp_sum(p0 + p1);
       m[r] = mn;
 #pragma unroll
