@@ -164,6 +164,22 @@ def _kernel_numbers(timer: _Timer, hbm_gbs: float, tflops: float) -> List[dict]:
         nbytes = q.numel() * 2 * 2 + B * min(S, W + Q) * Gk * Dh * 2 * 2
         rec("window_attention (general kernel)", "prefill" if Q > 1 else "decode", f"B{B} S{S} q{Q} H{H} G{Gk} D{Dh} window{W} cap bias sink", ms, nbytes,
             "paged_attention impl=1 (the framework's kernel for head sizes other than 128)", like, flops=4.0 * B * keys * H * Dh)
+        # what bf16 serving runs for these heads: the same rows laid out 128 columns wide (zeros behind the 64 values) on the tcgen05 kernels
+        kp = torch.nn.functional.pad(k4, (0, 128 - Dh)).contiguous()
+        vp = torch.nn.functional.pad(v4, (0, 128 - Dh)).contiguous()
+        qp = torch.nn.functional.pad(q, (0, 128 - Dh)).contiguous()
+        lse = torch.empty(B * Q, H, dtype=torch.float32, device=dev)
+        ns = 1 if Q > 1 else 4
+
+        def padded_tc():
+            o = ops.paged_attention(qp, kp, vp, pt, slots, sl, cu, None if Q == 1 else ql, Q, ps, Dh ** -0.5, True, W, 30.0, num_splits=ns, lse=lse,
+                                    slopes=slopes)
+            return (o[:, :, :Dh].float() * torch.sigmoid(lse - sinks[None, :]).unsqueeze(-1)).to(o.dtype)
+
+        ms3 = timer(padded_tc)
+        rec("window attention, 64-wide heads laid out 128 wide on the tcgen05 kernels", "prefill" if Q > 1 else "decode",
+            f"B{B} S{S} q{Q} H{H} G{Gk} D{Dh}->128 window{W} cap bias sink splits{ns}", ms3, 2 * nbytes, "window_attention (general kernel) on the plain layout",
+            ms, like_bytes=nbytes, flops=4.0 * B * keys * H * Dh)
     Dh = 128
     # ---- q/k norm + cache write
     T = 8192

@@ -344,31 +344,34 @@ void mamba2_scan(const at::Tensor& u, c10::optional<at::Tensor> z, const at::Ten
 }
 
 void qk_norm_cache_write(const at::Tensor& qkv, int64_t H, int64_t G, int64_t D, int64_t Dv, const at::Tensor& positions, double eps, double temp_coef,
-                         int64_t temp_every, at::Tensor k_cache, at::Tensor v_cache, const at::Tensor& loc, bool normalise, at::Tensor q_out) {
+                         int64_t temp_every, at::Tensor k_cache, at::Tensor v_cache, const at::Tensor& loc, bool normalise, at::Tensor q_out, int64_t pad) {
   CHECK_CUDA(qkv); CHECK_I32(positions); CHECK_I32(loc);
   TORCH_CHECK(bf16_or_f32(qkv) && qkv.dim() == 2 && qkv.stride(1) == 1 && qkv.size(1) == (H + G) * D + G * Dv);
   TORCH_CHECK(k_cache.scalar_type() == qkv.scalar_type() && v_cache.scalar_type() == qkv.scalar_type() && q_out.scalar_type() == qkv.scalar_type() &&
-              q_out.is_contiguous() && q_out.numel() == qkv.size(0) * H * D);
+              q_out.is_contiguous() && q_out.numel() == qkv.size(0) * H * (pad > 0 ? pad : D) && (pad == 0 || (pad >= D && pad >= Dv)));
   TORCH_CHECK(k_cache.dim() == 3 && k_cache.size(1) == 1 && k_cache.stride(2) == 1 && v_cache.stride(2) == 1 && k_cache.stride(0) == v_cache.stride(0) &&
-              k_cache.size(2) >= G * D && v_cache.size(2) >= G * Dv && temp_every >= 1 && positions.numel() == qkv.size(0) && loc.numel() == qkv.size(0));
+              k_cache.size(2) >= G * (pad > 0 ? pad : D) && v_cache.size(2) >= G * (pad > 0 ? pad : Dv) && temp_every >= 1 && positions.numel() == qkv.size(0) && loc.numel() == qkv.size(0));
   if (qkv.size(0) == 0) return;
   c10::cuda::CUDAGuard g(qkv.device());
   sglb::qk_norm_cache_write(qkv.data_ptr(), (int)qkv.stride(0), qkv.scalar_type() == at::kBFloat16, (int)qkv.size(0), (int)H, (int)G, (int)D, (int)Dv,
                             positions.data_ptr<int>(), (float)eps, (float)temp_coef, (int)temp_every, k_cache.data_ptr(), v_cache.data_ptr(),
-                            (size_t)k_cache.stride(0), loc.data_ptr<int>(), normalise, q_out.data_ptr(), cur_stream());
+                            (size_t)k_cache.stride(0), loc.data_ptr<int>(), normalise, q_out.data_ptr(), (int)pad, cur_stream());
   count();
 }
 
 void window_attention(const at::Tensor& q, const at::Tensor& k_cache, const at::Tensor& v_cache, int64_t G, int64_t Dv, const at::Tensor& page_table,
                       const at::Tensor& req_slots, const at::Tensor& seq_lens, c10::optional<at::Tensor> cu_q, int64_t max_q_len, int64_t page_size,
-                      double scale, double softcap, int64_t window, c10::optional<at::Tensor> slopes, c10::optional<at::Tensor> sinks, at::Tensor out) {
+                      double scale, double softcap, int64_t window, c10::optional<at::Tensor> slopes, c10::optional<at::Tensor> sinks, at::Tensor out,
+                      int64_t dim, int64_t pad) {
   CHECK_CUDA(q); CHECK_I32(page_table); CHECK_I32(req_slots); CHECK_I32(seq_lens);
   TORCH_CHECK(bf16_or_f32(q) && q.dim() == 3 && q.is_contiguous() && out.is_contiguous() && out.scalar_type() == q.scalar_type() &&
               out.numel() == q.size(0) * q.size(1) * Dv);
-  const int64_t H = q.size(1), D = q.size(2);
+  // pad > 0: q [T, H, pad] and every key / value head occupy ``pad`` columns of which the first ``dim`` / ``Dv`` count
+  const int64_t H = q.size(1), D = pad > 0 ? dim : q.size(2);
+  TORCH_CHECK(pad == 0 || (q.size(2) == pad && D >= 1 && D <= pad && Dv <= pad));
   TORCH_CHECK(k_cache.scalar_type() == q.scalar_type() && v_cache.scalar_type() == q.scalar_type() && k_cache.dim() == 3 && k_cache.size(1) == 1 &&
-              k_cache.stride(2) == 1 && v_cache.stride(2) == 1 && k_cache.stride(0) == v_cache.stride(0) && k_cache.size(2) >= G * D &&
-              v_cache.size(2) >= G * Dv && page_table.dim() == 2 && page_table.stride(1) == 1 && G >= 1 && H % G == 0);
+              k_cache.stride(2) == 1 && v_cache.stride(2) == 1 && k_cache.stride(0) == v_cache.stride(0) && k_cache.size(2) >= G * (pad > 0 ? pad : D) &&
+              v_cache.size(2) >= G * (pad > 0 ? pad : Dv) && page_table.dim() == 2 && page_table.stride(1) == 1 && G >= 1 && H % G == 0);
   const int B = (int)req_slots.size(0);
   if (cu_q.has_value()) { CHECK_I32(*cu_q); TORCH_CHECK(cu_q->numel() == B + 1); } else TORCH_CHECK(q.size(0) == B);
   if (sinks.has_value()) TORCH_CHECK(sinks->scalar_type() == at::kFloat && sinks->is_contiguous() && sinks->numel() == H);
@@ -378,7 +381,7 @@ void window_attention(const at::Tensor& q, const at::Tensor& k_cache, const at::
   sglb::window_attention(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), q.scalar_type() == at::kBFloat16, (size_t)k_cache.stride(0), (int)H, (int)G,
                          (int)D, (int)Dv, page_table.data_ptr<int>(), (int)page_table.stride(0), (int)page_size, req_slots.data_ptr<int>(),
                          seq_lens.data_ptr<int>(), opt_ptr<int>(cu_q), B, cu_q.has_value() ? (int)max_q_len : 1, (float)scale, (float)softcap, (int)window,
-                         opt_ptr<float>(slopes), opt_ptr<float>(sinks), out.data_ptr(), cur_stream());
+                         opt_ptr<float>(slopes), opt_ptr<float>(sinks), out.data_ptr(), (int)pad, cur_stream());
   count();
 }
 
@@ -859,9 +862,10 @@ TORCH_LIBRARY(sglb, m) {
   m.def("mamba2_scan(Tensor u, Tensor? z, Tensor dt_raw, Tensor dt_bias, Tensor A_log, Tensor? D, Tensor(a!) state, Tensor req_slots, Tensor seq_lens, "
         "Tensor? cu_q, int H, int P, int N, int G, Tensor(b!) out) -> ()", &mamba2_scan);
   m.def("qk_norm_cache_write(Tensor qkv, int H, int G, int D, int Dv, Tensor positions, float eps, float temp_coef, int temp_every, "
-        "Tensor(a!) k_cache, Tensor(b!) v_cache, Tensor loc, bool normalise, Tensor(c!) q_out) -> ()", &qk_norm_cache_write);
+        "Tensor(a!) k_cache, Tensor(b!) v_cache, Tensor loc, bool normalise, Tensor(c!) q_out, int pad=0) -> ()", &qk_norm_cache_write);
   m.def("window_attention(Tensor q, Tensor k_cache, Tensor v_cache, int G, int Dv, Tensor page_table, Tensor req_slots, Tensor seq_lens, Tensor? cu_q, "
-        "int max_q_len, int page_size, float scale, float softcap, int window, Tensor? slopes, Tensor? sinks, Tensor(a!) out) -> ()", &window_attention);
+        "int max_q_len, int page_size, float scale, float softcap, int window, Tensor? slopes, Tensor? sinks, Tensor(a!) out, int dim=0, int pad=0) -> ()",
+        &window_attention);
   m.def("moe_softmax_bias_route(Tensor logits, Tensor? corr, int n_real, Tensor(a!) w, Tensor(b!) ids, Tensor(c!) ident) -> ()", &moe_softmax_bias_route);
   m.def("moe_identity_shared_combine(Tensor(a!) y, Tensor h, Tensor? ident, Tensor? shared, Tensor? gate) -> ()", &moe_identity_shared_combine);
   m.def("gated_delta_rule(Tensor u, int Hk, int Dk, int H, int Dv, Tensor a_raw, Tensor A_log, Tensor dt_bias, Tensor b_raw, Tensor(a!) state, "

@@ -35,7 +35,7 @@ template <typename T>
 __global__ void __launch_bounds__(128) qk_norm_cache_write_kernel(const T* __restrict__ qkv, int ld, int H, int G, int D, int Dv,
                                                                   const int* __restrict__ positions, float eps, float coef, int every,
                                                                   T* __restrict__ kc, T* __restrict__ vc, size_t ldc, const int* __restrict__ loc,
-                                                                  int normalise, T* __restrict__ q_out) {
+                                                                  int normalise, T* __restrict__ q_out, int Dq, int hsk, int hsv) {
   const int t = blockIdx.x;
   const T* row = qkv + (size_t)t * ld;
   const size_t slot = (size_t)loc[t];
@@ -52,17 +52,23 @@ __global__ void __launch_bounds__(128) qk_norm_cache_write_kernel(const T* __res
     ss = warp_sum(ss);
     float mult = normalise ? 1.0f / sqrtf(ss / (float)D + eps) : 1.f;
     T* dst;
+    int width;                      // head stride of the destination: columns beyond D are zero padding
     if (hd < H) {
-      dst = q_out + ((size_t)t * H + hd) * D;
+      dst = q_out + ((size_t)t * H + hd) * Dq;
+      width = Dq;
       mult *= temp;
     } else {
-      dst = kc + slot * ldc + (size_t)(hd - H) * D;
+      dst = kc + slot * ldc + (size_t)(hd - H) * hsk;
+      width = hsk;
     }
-    for (int i = lane; i < D; i += 32) wa_st<T>(dst + i, wa_ld<T>(src + i) * mult);
+    for (int i = lane; i < width; i += 32) wa_st<T>(dst + i, i < D ? wa_ld<T>(src + i) * mult : 0.f);
   }
   const T* vs = row + (size_t)(H + G) * D;
   T* vd = vc + slot * ldc;
-  for (int i = threadIdx.x; i < G * Dv; i += 128) vd[i] = vs[i];
+  for (int i = threadIdx.x; i < G * hsv; i += 128) {
+    const int gh = i / hsv, c = i - gh * hsv;
+    wa_st<T>(vd + i, c < Dv ? wa_ld<T>(vs + gh * Dv + c) : 0.f);
+  }
 }
 
 constexpr int WA_KT = 64;        // keys per tile
@@ -76,6 +82,7 @@ struct WinAttnParams {
   const int* req_slots; const int* seq_lens; const int* cu_q;
   const float* slopes; const float* sinks;
   int H, G, HG, HC, nchunks, QT, D, Dp, Dv;
+  int Dq, hsk, hsv;                            // head strides of q and of the key / value rows (>= D, D, Dv: padded layouts)
   float scale, softcap; int window;
   int vec;                                     // 16-byte gathers: head sizes, row stride and base addresses allow them
 };
@@ -118,7 +125,7 @@ __global__ void __launch_bounds__(WA_NT) window_attention_kernel(const WinAttnPa
     const int r = idx / Dp, d = idx - r * Dp;
     const int qi = r / HC, hc = r - qi * HC;
     float v = 0.f;
-    if (qi < nq && hc < nh && d < D) v = wa_ld<T>(qg + ((size_t)(q0 + qt0 + qi) * p.H + hbase + hc) * D + d) * p.scale;
+    if (qi < nq && hc < nh && d < D) v = wa_ld<T>(qg + ((size_t)(q0 + qt0 + qi) * p.H + hbase + hc) * p.Dq + d) * p.scale;
     sQ[idx] = v;
   }
   // ---- per-row constants and online soft-max state (the sink is the first term: max = sink, sum = 1)
@@ -157,7 +164,7 @@ __global__ void __launch_bounds__(WA_NT) window_attention_kernel(const WinAttnPa
         const int s = sSlot[jj];
         float* dst = sK + jj * ldk + ch * EPV;
         if (s >= 0) {
-          wa_load16(kg + (size_t)s * p.ldc + (size_t)g * D + ch * EPV, dst);
+          wa_load16(kg + (size_t)s * p.ldc + (size_t)g * p.hsk + ch * EPV, dst);
         } else {
 #pragma unroll
           for (int e = 0; e < EPV; ++e) dst[e] = 0.f;
@@ -168,7 +175,7 @@ __global__ void __launch_bounds__(WA_NT) window_attention_kernel(const WinAttnPa
         const int s = sSlot[jj];
         float* dst = sV + jj * ldv + ch * EPV;
         if (s >= 0) {
-          wa_load16(vg + (size_t)s * p.ldc + (size_t)g * Dv + ch * EPV, dst);
+          wa_load16(vg + (size_t)s * p.ldc + (size_t)g * p.hsv + ch * EPV, dst);
         } else {
 #pragma unroll
           for (int e = 0; e < EPV; ++e) dst[e] = 0.f;
@@ -178,12 +185,12 @@ __global__ void __launch_bounds__(WA_NT) window_attention_kernel(const WinAttnPa
       for (int idx = tid; idx < WA_KT * Dp; idx += WA_NT) {
         const int jj = idx / Dp, d = idx - jj * Dp;
         const int s = sSlot[jj];
-        sK[jj * ldk + d] = (s >= 0 && d < D) ? wa_ld<T>(kg + (size_t)s * p.ldc + (size_t)g * D + d) : 0.f;
+        sK[jj * ldk + d] = (s >= 0 && d < D) ? wa_ld<T>(kg + (size_t)s * p.ldc + (size_t)g * p.hsk + d) : 0.f;
       }
       for (int idx = tid; idx < WA_KT * ldv; idx += WA_NT) {
         const int jj = idx / ldv, c = idx - jj * ldv;
         const int s = sSlot[jj];
-        sV[idx] = (s >= 0 && c < Dv) ? wa_ld<T>(vg + (size_t)s * p.ldc + (size_t)g * Dv + c) : 0.f;
+        sV[idx] = (s >= 0 && c < Dv) ? wa_ld<T>(vg + (size_t)s * p.ldc + (size_t)g * p.hsv + c) : 0.f;
       }
     }
     __syncthreads();
@@ -286,20 +293,21 @@ void dispatch_wa(const WinAttnParams& p, int B, int max_q_len, cudaStream_t stre
 }  // namespace
 
 void qk_norm_cache_write(const void* qkv, int ld, bool bf16, int T, int H, int G, int D, int Dv, const int* positions, float eps, float coef, int every,
-                         void* kc, void* vc, size_t ldc, const int* loc, bool normalise, void* q_out, cudaStream_t stream) {
+                         void* kc, void* vc, size_t ldc, const int* loc, bool normalise, void* q_out, int pad, cudaStream_t stream) {
   if (T <= 0) return;
+  const int Dq = pad > 0 ? pad : D, hsk = pad > 0 ? pad : D, hsv = pad > 0 ? pad : Dv;      // pad: every head occupies ``pad`` columns, zeros behind its values
   if (bf16)
     qk_norm_cache_write_kernel<__nv_bfloat16><<<T, 128, 0, stream>>>((const __nv_bfloat16*)qkv, ld, H, G, D, Dv, positions, eps, coef, every,
-                                                                     (__nv_bfloat16*)kc, (__nv_bfloat16*)vc, ldc, loc, normalise ? 1 : 0, (__nv_bfloat16*)q_out);
+                                                                     (__nv_bfloat16*)kc, (__nv_bfloat16*)vc, ldc, loc, normalise ? 1 : 0, (__nv_bfloat16*)q_out, Dq, hsk, hsv);
   else
     qk_norm_cache_write_kernel<float><<<T, 128, 0, stream>>>((const float*)qkv, ld, H, G, D, Dv, positions, eps, coef, every, (float*)kc, (float*)vc, ldc,
-                                                             loc, normalise ? 1 : 0, (float*)q_out);
+                                                             loc, normalise ? 1 : 0, (float*)q_out, Dq, hsk, hsv);
   SGLB_CUDA_CHECK(cudaGetLastError());
 }
 
 void window_attention(const void* q, const void* kc, const void* vc, bool bf16, size_t ldc, int H, int G, int D, int Dv, const int* page_table,
                       int pt_stride, int page_size, const int* req_slots, const int* seq_lens, const int* cu_q, int B, int max_q_len, float scale,
-                      float softcap, int window, const float* slopes, const float* sinks, void* out, cudaStream_t stream) {
+                      float softcap, int window, const float* slopes, const float* sinks, void* out, int pad, cudaStream_t stream) {
   if (B <= 0 || max_q_len <= 0) return;
   if (D > 256 || Dv > 256 || B > 65535 || H % G) throw std::runtime_error("sglb window_attention: head sizes up to 256, heads a multiple of key heads");
   WinAttnParams p;
@@ -311,10 +319,11 @@ void window_attention(const void* q, const void* kc, const void* vc, bool bf16, 
   p.nchunks = (p.HG + p.HC - 1) / p.HC;
   p.QT = std::max(1, WA_ROWS / p.HC);
   p.D = D; p.Dp = (D + 3) / 4 * 4; p.Dv = Dv;
+  p.Dq = pad > 0 ? pad : D; p.hsk = pad > 0 ? pad : D; p.hsv = pad > 0 ? pad : Dv;
   p.scale = scale; p.softcap = softcap; p.window = window;
   const size_t esz = bf16 ? 2 : 4;
   const int epv = (int)(16 / esz);
-  p.vec = (D % epv == 0 && Dv % epv == 0 && (ldc * esz) % 16 == 0 && ((uintptr_t)kc % 16) == 0 && ((uintptr_t)vc % 16) == 0) ? 1 : 0;
+  p.vec = (D % epv == 0 && Dv % epv == 0 && p.hsk % epv == 0 && p.hsv % epv == 0 && (ldc * esz) % 16 == 0 && ((uintptr_t)kc % 16) == 0 && ((uintptr_t)vc % 16) == 0) ? 1 : 0;
   if (p.G * p.nchunks > 65535) throw std::runtime_error("sglb window_attention: too many heads for one launch");
   if (bf16) dispatch_wa<__nv_bfloat16>(p, B, max_q_len, stream);
   else dispatch_wa<float>(p, B, max_q_len, stream);

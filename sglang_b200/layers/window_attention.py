@@ -8,9 +8,12 @@
 The projections are one GEMM with their biases in the epilogue; ``ops.qk_norm_cache_write`` normalises q and k, applies the query
 temperature and writes k / v rows into the paged pool; ``ops.window_attention`` (csrc/kernels/window_attention.cu) is the attention itself,
 one kernel for prompt portions and decode tokens.  Cap, bias, mask, sink and soft-max are fp32; the cache is in the model dtype.  bf16
-models whose key and value heads are both 128 wide run the framework's tcgen05 attention kernels instead (``ops.paged_attention`` with
-``slopes``: the distance bias joins their score pass behind the cap, the sink enters through the log-sum-exp); every other size, and fp32
-serving, stays on the general kernel.
+models whose key and value heads are at most 128 wide run the framework's tcgen05 attention kernels instead (``ops.paged_attention`` with
+``slopes``: the distance bias joins their score pass behind the cap, the sink enters through the log-sum-exp).  Those kernels have 128-wide
+heads, so such a layer lays its heads out 128 columns wide in q and in the cache rows, zeros behind the values (``pad``): the scores do not
+change, the output's first ``vdim`` columns are the result, and a 64-wide head pays twice the cache bytes and tensor-core work for leaving
+the CUDA-core kernel (about 3x faster on prompts at that size).  Every other size (heads wider than 128, group sizes that do not divide 128),
+fp32 serving, and any call the tcgen05 kernels do not take stay on the general kernel, which reads the same layout.
 
 The paged pool holds one flat row per token and plane (``cache_width`` columns, the widest layer's ``kv_heads * max(dim, vdim)``): a layer
 reads the first ``kv_heads * dim`` columns of the key plane as its key heads, so layers of different head counts and sizes share one pool.
@@ -60,10 +63,15 @@ class BiasedWindowAttention(nn.Module):
         self.o_weight = nn.Parameter(torch.zeros(width, heads * vdim, dtype=dtype), requires_grad=False)
         self.sinks = nn.Parameter(torch.zeros(heads, dtype=torch.float32), requires_grad=False) if sinks else None
         self.slopes = nn.Parameter(distance_slopes(heads), requires_grad=False) if distance_bias else None
+        self.pad = 0                 # 128: heads laid out 128 columns wide for the tcgen05 kernels (the model decides, see ``wants_padding``)
+
+    def wants_padding(self, dtype) -> bool:
+        """whether this layer would run the tcgen05 kernels if its pool rows are ``kv_heads * 128`` wide"""
+        return bool(self.tc_route and dtype == torch.bfloat16 and self.D <= 128 and self.Dv <= 128 and 128 % (self.H // self.G) == 0)
 
     @property
     def cache_width(self) -> int:
-        return self.G * max(self.D, self.Dv)
+        return self.G * (self.pad if self.pad else max(self.D, self.Dv))
 
     def load(self, leaf: str, w: torch.Tensor) -> bool:
         hd, gd = self.H * self.D, self.G * self.D
@@ -86,9 +94,10 @@ class BiasedWindowAttention(nn.Module):
         T = h.shape[0]
         qkv = ops.linear(h, self.qkv_weight, self.qkv_bias)
         kc, vc = fb.kv_pool.k(cache_idx), fb.kv_pool.v(cache_idx)                  # [slots, 1, cache_width] each
+        pad = self.pad
         q = ops.qk_norm_cache_write(qkv, self.H, self.G, self.D, self.Dv, fb.positions, self.eps, self.temp_coef, self.temp_every, kc, vc,
-                                    fb.out_cache_loc, self.qk_norm)
-        if self.tc_route and self.D == 128 and self.Dv == 128 and kc.shape[-1] == self.G * 128:
+                                    fb.out_cache_loc, self.qk_norm, pad)
+        if pad == 128 and kc.shape[-1] == self.G * 128:
             k4, v4 = kc.view(-1, self.G, 128), vc.view(-1, self.G, 128)
             if ops.tc_attention_ok(q, k4, v4, fb.page_size):
                 # bf16, 128-wide heads: the framework's tcgen05 attention kernels (prompt tiles and split-KV decode) with the bias folded into
@@ -98,9 +107,11 @@ class BiasedWindowAttention(nn.Module):
                 o = ops.paged_attention(q, k4, v4, fb.page_table, fb.req_slots, fb.seq_lens, fb.cu_q, fb.q_lens, fb.max_q_len, fb.page_size, self.scale,
                                         causal=True, window=self.window, logit_cap=self.softcap, num_splits=fb.num_splits if dec else 1,
                                         workspace=fb.attn_workspace if dec else None, lse=lse, slopes=self.slopes)
+                if self.Dv < 128:
+                    o = o[:, :, : self.Dv]
                 if lse is not None:
                     o = (o.float() * torch.sigmoid(lse - self.sinks[None, :]).unsqueeze(-1)).to(o.dtype)
-                return ops.linear(o.view(T, self.H * self.Dv), self.o_weight)
+                return ops.linear(o.reshape(T, self.H * self.Dv), self.o_weight)
         o = ops.window_attention(q, kc, vc, self.G, self.Dv, fb.page_table, fb.req_slots, fb.seq_lens, fb.cu_q, fb.q_lens, fb.max_q_len, fb.page_size,
-                                 self.scale, self.softcap, self.window, self.slopes, self.sinks)
+                                 self.scale, self.softcap, self.window, self.slopes, self.sinks, self.D, pad)
         return ops.linear(o.view(T, self.H * self.Dv), self.o_weight)

@@ -182,7 +182,13 @@ class ZaparaxForCausalLM(nn.Module):
         bb.all_layers = nn.ModuleList([ZaparaxBlock(cfg, s, i, dtype) for i, s in enumerate(specs)])
         # runs: (block index, index of the run's cache layer or state entry); what is looped gets a fresh index every pass
         self.runs: List[Tuple[int, int]] = []
-        cache_width = max([b.mix.cache_width for b in bb.all_layers if b.kind == "attention"] or [0])
+        # bf16 layers whose heads fit the tcgen05 kernels lay them out 128 columns wide, when that is also the pool's row width (the widest layer's)
+        attn = [b.mix for b in bb.all_layers if b.kind == "attention"]
+        widest = max([m.G * 128 if m.wants_padding(dtype) else m.cache_width for m in attn] or [0])
+        for m in attn:
+            if m.wants_padding(dtype) and m.G * 128 == widest:
+                m.pad = 128
+        cache_width = max([m.cache_width for m in attn] or [0])
         bb.layers, n_rec = [], 0           # ``layers``: what the runner sizes the paged pool from (one entry per attention run)
         for i in layer_runs(len(specs), cfg.hybrid.get("loop")):
             blk = bb.all_layers[i]

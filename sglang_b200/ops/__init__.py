@@ -570,29 +570,34 @@ def mamba2_scan(u: torch.Tensor, z: Optional[torch.Tensor], dt_raw: torch.Tensor
 
 
 def qk_norm_cache_write(qkv: torch.Tensor, H: int, G: int, D: int, Dv: int, positions: torch.Tensor, eps: float, temp_coef: float, temp_every: int,
-                        k_cache: torch.Tensor, v_cache: torch.Tensor, out_cache_loc: torch.Tensor, normalise: bool = True) -> torch.Tensor:
+                        k_cache: torch.Tensor, v_cache: torch.Tensor, out_cache_loc: torch.Tensor, normalise: bool = True, pad: int = 0) -> torch.Tensor:
     """per-head unit-RMS q and k, position-dependent query temperature, and the write of k / v rows into the paged cache, one kernel
-    (csrc/kernels/window_attention.cu; semantics in ``torch_ref.qk_norm_cache_write``).  Returns q [T, H, D] in the cache dtype."""
+    (csrc/kernels/window_attention.cu; semantics in ``torch_ref.qk_norm_cache_write``).  Returns q [T, H, D] in the cache dtype.
+    ``pad > 0``: every head of q, k and v is laid out ``pad`` columns wide with zeros behind its values (the tcgen05 kernels' head size)."""
     if (_use_native(qkv) and qkv.dtype in (torch.bfloat16, torch.float32) and qkv.is_contiguous() and k_cache.dtype == qkv.dtype and v_cache.dtype == qkv.dtype
             and k_cache.stride(-1) == 1 and v_cache.stride(-1) == 1 and k_cache.stride(0) == v_cache.stride(0)):
-        q = torch.empty(qkv.shape[0], H, D, dtype=qkv.dtype, device=qkv.device)
+        q = torch.empty(qkv.shape[0], H, pad if pad > 0 else D, dtype=qkv.dtype, device=qkv.device)
         torch.ops.sglb.qk_norm_cache_write(qkv, int(H), int(G), int(D), int(Dv), positions, float(eps), float(temp_coef), int(max(1, temp_every)), k_cache,
-                                           v_cache, out_cache_loc, bool(normalise), q)
+                                           v_cache, out_cache_loc, bool(normalise), q, int(pad))
         return q
-    return torch_ref.qk_norm_cache_write(qkv, H, G, D, Dv, positions, eps, temp_coef, max(1, temp_every), k_cache, v_cache, out_cache_loc, normalise)
+    return torch_ref.qk_norm_cache_write(qkv, H, G, D, Dv, positions, eps, temp_coef, max(1, temp_every), k_cache, v_cache, out_cache_loc, normalise, pad)
 
 
 def window_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, G: int, Dv: int, page_table: torch.Tensor, req_slots: torch.Tensor,
                      seq_lens: torch.Tensor, cu_q: Optional[torch.Tensor], q_lens: Optional[torch.Tensor], max_q_len: int, page_size: int, scale: float,
-                     softcap: float = 0.0, window: int = -1, slopes: Optional[torch.Tensor] = None, sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
+                     softcap: float = 0.0, window: int = -1, slopes: Optional[torch.Tensor] = None, sinks: Optional[torch.Tensor] = None,
+                     dim: int = 0, pad: int = 0) -> torch.Tensor:
     """paged grouped-query attention with a tanh score cap, a per-head distance bias, a sliding window and soft-max sinks, for prompt portions
-    and decode tokens (csrc/kernels/window_attention.cu; semantics in ``torch_ref.window_attention``).  Returns [T, H, Dv] in q's dtype."""
+    and decode tokens (csrc/kernels/window_attention.cu; semantics in ``torch_ref.window_attention``).  Returns [T, H, Dv] in q's dtype.
+    ``pad > 0``: heads are laid out ``pad`` columns wide in q and in the cache rows; ``dim`` is the key size that counts."""
     T, H, D = q.shape
+    if pad > 0:
+        D = dim
     if (_use_native(q) and q.dtype in (torch.bfloat16, torch.float32) and q.is_contiguous() and k_cache.dtype == q.dtype and v_cache.dtype == q.dtype
             and D <= 256 and Dv <= 256 and req_slots.numel() <= 65535 and k_cache.stride(0) == v_cache.stride(0)):
         out = torch.empty(T, H, Dv, dtype=q.dtype, device=q.device)
         torch.ops.sglb.window_attention(q, k_cache, v_cache, int(G), int(Dv), page_table, req_slots, seq_lens, cu_q, int(max_q_len), int(page_size),
-                                        float(scale), float(softcap), int(window), slopes, sinks, out)
+                                        float(scale), float(softcap), int(window), slopes, sinks, out, int(D), int(pad))
         return out
     return torch_ref.window_attention(q, k_cache, v_cache, G, Dv, page_table, req_slots, seq_lens, q_lens, page_size, scale, softcap, window, slopes,
-                                      sinks).to(q.dtype)
+                                      sinks, dim, pad).to(q.dtype)

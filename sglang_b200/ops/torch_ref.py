@@ -562,10 +562,11 @@ def mamba2_scan(u: torch.Tensor, z: Optional[torch.Tensor], dt_raw: torch.Tensor
 
 
 def qk_norm_cache_write(qkv: torch.Tensor, H: int, G: int, D: int, Dv: int, positions: torch.Tensor, eps: float, temp_coef: float, temp_every: int,
-                        k_cache: torch.Tensor, v_cache: torch.Tensor, out_cache_loc: torch.Tensor, normalise: bool = True) -> torch.Tensor:
+                        k_cache: torch.Tensor, v_cache: torch.Tensor, out_cache_loc: torch.Tensor, normalise: bool = True, pad: int = 0) -> torch.Tensor:
     """qkv [T, H*D + G*D + G*Dv] -> q [T, H, D] (cache dtype) with every head divided by its root mean square and multiplied by the
     position's query temperature ``1 + coef * ln(floor((p + 1) / every) + 1)``; the heads of k (same unit-RMS form) go to the first
-    ``G*D`` columns of ``k_cache[loc]`` and v to the first ``G*Dv`` columns of ``v_cache[loc]`` (caches [slots, 1, width])."""
+    ``G*D`` columns of ``k_cache[loc]`` and v to the first ``G*Dv`` columns of ``v_cache[loc]`` (caches [slots, 1, width]).
+    ``pad > 0``: every head of q, k and v occupies ``pad`` columns, zeros behind its values (q is [T, H, pad])."""
     T = qkv.shape[0]
     q = qkv[:, :H * D].float().view(T, H, D)
     k = qkv[:, H * D:H * D + G * D].float().view(T, G, D)
@@ -577,6 +578,11 @@ def qk_norm_cache_write(qkv: torch.Tensor, H: int, G: int, D: int, Dv: int, posi
         p1 = positions.long() + 1
         q = q * (1.0 + temp_coef * torch.log((p1 // int(temp_every)).float() + 1.0))[:, None, None]
     loc = out_cache_loc.long()
+    if pad > 0:
+        zp = lambda t, n: torch.nn.functional.pad(t, (0, pad - n))
+        k_cache[loc, 0, :G * pad] = zp(k, D).reshape(T, G * pad).to(k_cache.dtype)
+        v_cache[loc, 0, :G * pad] = zp(v.view(T, G, Dv), Dv).reshape(T, G * pad).to(v_cache.dtype)
+        return zp(q, D).to(k_cache.dtype)
     k_cache[loc, 0, :G * D] = k.reshape(T, G * D).to(k_cache.dtype)
     v_cache[loc, 0, :G * Dv] = v.to(v_cache.dtype)
     return q.to(k_cache.dtype)
@@ -584,14 +590,19 @@ def qk_norm_cache_write(qkv: torch.Tensor, H: int, G: int, D: int, Dv: int, posi
 
 def window_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, G: int, Dv: int, page_table: torch.Tensor, req_slots: torch.Tensor,
                      seq_lens: torch.Tensor, q_lens: Optional[torch.Tensor], page_size: int, scale: float, softcap: float, window: int,
-                     slopes: Optional[torch.Tensor], sinks: Optional[torch.Tensor]) -> torch.Tensor:
+                     slopes: Optional[torch.Tensor], sinks: Optional[torch.Tensor], dim: int = 0, pad: int = 0) -> torch.Tensor:
     """grouped-query attention over a paged cache with a tanh score cap, a per-head distance bias, a sliding window and soft-max sinks.
+    ``pad > 0``: q is [T, H, pad] and every key / value head occupies ``pad`` cache columns, of which the first ``dim`` / ``Dv`` count.
 
     q [T, H, D]; caches [slots, 1, width] with the G key heads in the first ``G*D`` columns (values: ``G*Dv``); query head h reads key head
     ``h // (H // G)``.  score_ij = cap(q_i . k_j * scale) - slopes_h * (i - j) with cap(s) = softcap * tanh(s / softcap) (``softcap <= 0``:
     none); key j is visible when ``0 <= i - j < window`` (``window <= 0``: all earlier keys); ``sinks`` fp32 [H]: exp(sink_h) joins the
     soft-max denominator only.  Returns fp32 [T, H, Dv]."""
     T, H, D = q.shape
+    if pad > 0:
+        D = dim
+        q = q[:, :, :D]
+    hk, hv = (pad, pad) if pad > 0 else (D, Dv)
     rep = H // G
     out = torch.empty(T, H, Dv, dtype=torch.float32, device=q.device)
     qs = 0
@@ -603,8 +614,8 @@ def window_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
         lo = 0 if window <= 0 else max(0, L - ql - window + 1)
         pos = torch.arange(lo, L, device=q.device)
         slots = page_table[int(req_slots[b]), (pos // page_size).long()].long() * page_size + pos % page_size
-        K = k_cache[slots, 0, :G * D].float().view(-1, G, D).repeat_interleave(rep, 1)
-        V = v_cache[slots, 0, :G * Dv].float().view(-1, G, Dv).repeat_interleave(rep, 1)
+        K = k_cache[slots, 0, :G * hk].float().view(-1, G, hk)[:, :, :D].repeat_interleave(rep, 1)
+        V = v_cache[slots, 0, :G * hv].float().view(-1, G, hv)[:, :, :Dv].repeat_interleave(rep, 1)
         s = torch.einsum("qhd,khd->hqk", q[qs:qs + ql].float(), K) * scale
         if softcap > 0:
             s = softcap * torch.tanh(s / softcap)

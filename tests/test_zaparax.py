@@ -252,6 +252,28 @@ def test_window_attention_reference_op_edges_sink_and_bias():
         assert (out[0, 1, 0].item() > 1.0) == (qpos == mark + W - 1)
 
 
+def test_padded_head_layout_reference_ops():
+    """heads laid out 16 columns wide (zeros behind the values) give the same q, the same cache contents under the padding and the same output"""
+    g = torch.Generator().manual_seed(5)
+    H, G, D, Dv, ps, T, pad = 4, 2, 6, 5, 4, 21, 16
+    qkv = torch.randn(T, (H + G) * D + G * Dv, generator=g)
+    pos = torch.arange(T, dtype=torch.int32)
+    pt = torch.zeros(2, 8, dtype=torch.int32)
+    pt[1, :6] = torch.tensor([3, 1, 6, 2, 5, 4], dtype=torch.int32)
+    loc = (pt[1, (pos // ps).long()] * ps + pos % ps).int()
+    k1, v1 = torch.zeros(8 * ps, 1, G * 6), torch.zeros(8 * ps, 1, G * 6)
+    k2, v2 = torch.full((8 * ps, 1, G * pad), 9.0), torch.full((8 * ps, 1, G * pad), 9.0)          # stale numbers the padding has to overwrite
+    q1 = torch_ref.qk_norm_cache_write(qkv, H, G, D, Dv, pos, 1e-5, 0.3, 4, k1, v1, loc)
+    q2 = torch_ref.qk_norm_cache_write(qkv, H, G, D, Dv, pos, 1e-5, 0.3, 4, k2, v2, loc, True, pad)
+    assert q2.shape == (T, H, pad) and torch.equal(q2[:, :, :D], q1) and float(q2[:, :, D:].abs().max()) == 0.0
+    assert torch.equal(k2[loc.long(), 0].view(T, G, pad)[:, :, :D], k1[loc.long(), 0, :G * D].view(T, G, D))
+    assert float(k2[loc.long(), 0].view(T, G, pad)[:, :, D:].abs().max()) == 0.0 and float(v2[loc.long(), 0].view(T, G, pad)[:, :, Dv:].abs().max()) == 0.0
+    args = (pt, torch.tensor([1]), torch.tensor([T]), torch.tensor([T]), ps, 0.8, 3.0, 7, torch.tensor([0.5, 0.1, 0.03, 0.01]), torch.randn(H, generator=g))
+    o1 = torch_ref.window_attention(q1, k1, v1, G, Dv, *args)
+    o2 = torch_ref.window_attention(q2, k2, v2, G, Dv, *args, D, pad)
+    torch.testing.assert_close(o2, o1)
+
+
 def test_far_key_without_a_window():
     """no window: a key 300 positions back still wins when its score stands out (small slope head), and loses on the steep-slope head"""
     H, G, D, Dv, ps = 2, 1, 4, 2, 8

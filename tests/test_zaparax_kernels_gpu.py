@@ -195,6 +195,54 @@ def test_tensor_core_route_against_the_general_kernel(H, G, window, cap):
     both(q[last].contiguous(), None, None, 1, seq)
 
 
+@pytest.mark.parametrize("H,G,D,Dv,window,cap", [(8, 2, 64, 64, 100, 40.0), (4, 1, 96, 32, -1, 0.0), (16, 2, 40, 128, 300, 15.0)])
+def test_padded_heads_on_both_attention_routes(H, G, D, Dv, window, cap):
+    """bf16 heads narrower than 128 laid out 128 columns wide: the cache-write kernel pads with zeros over stale numbers, the general kernel
+    reads the padded layout like the plain one, and the tcgen05 kernels agree with it (prompt portions and decode)"""
+    _need()
+    g = torch.Generator().manual_seed(7)
+    ps, pad = 64, 128
+    q_lens, cached = [150, 1, 2, 260], [400, 300, 0, 0]
+    cu, seq = _ragged(q_lens, cached)
+    T = sum(q_lens)
+    pt, kc, vc = _paged(4, max(seq), ps, G * pad, torch.bfloat16, g)
+    slots = [1, 2, 3, 4]
+    kc1, vc1 = (torch.randn(kc.shape[0], 1, G * max(D, Dv), generator=g) * 0.5).to(torch.bfloat16), torch.randn(kc.shape[0], 1, G * max(D, Dv), generator=g).to(torch.bfloat16)
+    kc2, vc2 = kc.clone().to(DEV), vc.clone().to(DEV)                      # random (stale) numbers everywhere
+    kc1, vc1 = kc1.to(DEV), vc1.to(DEV)
+    # fill both layouts through the cache-write kernel: every position of every request
+    for b, L_ in enumerate(seq):
+        pos = torch.arange(L_, dtype=torch.int32)
+        loc = (pt[slots[b], (pos // ps).long()] * ps + pos % ps).int().to(DEV)
+        qkv = torch.randn(L_, (H + G) * D + G * Dv, generator=g).to(torch.bfloat16).to(DEV)
+        qa = ops.qk_norm_cache_write(qkv, H, G, D, Dv, pos.to(DEV), 1e-5, 0.2, 32, kc1, vc1, loc)
+        qb = ops.qk_norm_cache_write(qkv, H, G, D, Dv, pos.to(DEV), 1e-5, 0.2, 32, kc2, vc2, loc, True, pad)
+        assert torch.equal(qb[:, :, :D], qa) and float(qb[:, :, D:].float().abs().max()) == 0.0
+        rows, vrows = kc2[loc.long(), 0].view(L_, G, pad), vc2[loc.long(), 0].view(L_, G, pad)
+        assert float(rows[:, :, D:].float().abs().sum()) == 0.0 and float(vrows[:, :, Dv:].float().abs().sum()) == 0.0
+    q1 = torch.randn(T, H, D, generator=g).to(torch.bfloat16).to(DEV)
+    q2 = torch.nn.functional.pad(q1, (0, pad - D)).contiguous()
+    slopes = (2.0 ** (-8.0 * torch.arange(1, H + 1) / H)).float().to(DEV)
+    sinks = torch.randn(H, generator=g).to(DEV)
+    ptd = pt.to(DEV)
+    k4, v4 = kc2.view(-1, G, pad), vc2.view(-1, G, pad)
+    assert ops.tc_attention_ok(q2, k4, v4, ps)
+
+    def three(qa, qb, cu_q, ql, mq):
+        plain = ops.window_attention(qa, kc1, vc1, G, Dv, ptd, _i32(slots), _i32(seq), cu_q, ql, mq, ps, 0.11, cap, window, slopes, sinks).float()
+        padded = ops.window_attention(qb, kc2, vc2, G, Dv, ptd, _i32(slots), _i32(seq), cu_q, ql, mq, ps, 0.11, cap, window, slopes, sinks, D, pad).float()
+        torch.testing.assert_close(padded, plain, rtol=1e-2, atol=1e-2)
+        lse = torch.empty(qb.shape[0], H, dtype=torch.float32, device=DEV)
+        o = ops.paged_attention(qb, k4, v4, ptd, _i32(slots), _i32(seq), cu_q, ql, mq, ps, 0.11, True, window, cap, lse=lse, slopes=slopes)
+        tc = o[:, :, :Dv].float() * torch.sigmoid(lse - sinks[None, :]).unsqueeze(-1)
+        torch.testing.assert_close(tc, plain, rtol=3e-2, atol=3e-2)
+        assert (tc - plain).abs().mean().item() < 4e-3
+
+    three(q1, q2, _i32(cu), _i32(q_lens), max(q_lens))
+    last = torch.tensor([c - 1 for c in cu[1:]], device=DEV)
+    three(q1[last].contiguous(), q2[last].contiguous(), None, None, 1)
+
+
 def test_window_edge_on_the_kernel():
     """a key whose value stands out must count as the oldest key inside the window and vanish one step later, in a portion and in decode"""
     _need()
