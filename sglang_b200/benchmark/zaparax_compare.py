@@ -138,7 +138,7 @@ def _kernel_numbers(timer: _Timer, hbm_gbs: float, tflops: float) -> List[dict]:
         def tc_route():          # what bf16 serving with 128-wide heads runs: the same tcgen05 kernels with the bias in the score pass + the sink
             o = ops.paged_attention(q, k4, v4, pt, slots, sl, cu, None if Q == 1 else ql, Q, ps, Dh ** -0.5, True, W, 30.0, num_splits=ns, lse=lse,
                                     slopes=slopes)
-            return (o.float() * torch.sigmoid(lse - sinks[None, :]).unsqueeze(-1)).to(o.dtype)
+            return ops.attention_sink_gate(o, lse, sinks)
 
         ms2 = timer(tc_route)
         like2 = timer(lambda: ops.paged_attention(q, k4, v4, pt, slots, sl, cu, None if Q == 1 else ql, Q, ps, Dh ** -0.5, True, W, 30.0, num_splits=ns))
@@ -174,7 +174,7 @@ def _kernel_numbers(timer: _Timer, hbm_gbs: float, tflops: float) -> List[dict]:
         def padded_tc():
             o = ops.paged_attention(qp, kp, vp, pt, slots, sl, cu, None if Q == 1 else ql, Q, ps, Dh ** -0.5, True, W, 30.0, num_splits=ns, lse=lse,
                                     slopes=slopes)
-            return (o[:, :, :Dh].float() * torch.sigmoid(lse - sinks[None, :]).unsqueeze(-1)).to(o.dtype)
+            return ops.attention_sink_gate(o, lse, sinks, Dh)
 
         ms3 = timer(padded_tc)
         rec("window attention, 64-wide heads laid out 128 wide on the tcgen05 kernels", "prefill" if Q > 1 else "decode",

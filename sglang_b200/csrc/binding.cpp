@@ -385,6 +385,18 @@ void window_attention(const at::Tensor& q, const at::Tensor& k_cache, const at::
   count();
 }
 
+void attention_sink_gate(const at::Tensor& o, const at::Tensor& lse, const at::Tensor& sinks, int64_t Dv, at::Tensor out) {
+  CHECK_CUDA(o); CHECK_BF16(o); CHECK_BF16(out);
+  TORCH_CHECK(o.dim() == 3 && o.is_contiguous() && out.is_contiguous() && Dv >= 1 && Dv <= o.size(2) && out.numel() == o.size(0) * o.size(1) * Dv);
+  TORCH_CHECK(lse.scalar_type() == at::kFloat && lse.is_contiguous() && lse.numel() == o.size(0) * o.size(1) && sinks.scalar_type() == at::kFloat &&
+              sinks.is_contiguous() && sinks.numel() == o.size(1));
+  if (o.size(0) == 0) return;
+  c10::cuda::CUDAGuard g(o.device());
+  sglb::attention_sink_gate(o.data_ptr(), (int)o.size(2), lse.data_ptr<float>(), sinks.data_ptr<float>(), (int)(o.size(0) * o.size(1)), (int)o.size(1), (int)Dv,
+                            out.data_ptr(), cur_stream());
+  count();
+}
+
 void moe_softmax_bias_route(const at::Tensor& logits, c10::optional<at::Tensor> corr, int64_t n_real, at::Tensor w, at::Tensor ids, at::Tensor ident) {
   CHECK_CUDA(logits); CHECK_I32(ids);
   TORCH_CHECK(logits.scalar_type() == at::kFloat && logits.dim() == 2 && logits.stride(1) == 1 && w.scalar_type() == at::kFloat && w.is_contiguous() &&
@@ -866,6 +878,7 @@ TORCH_LIBRARY(sglb, m) {
   m.def("window_attention(Tensor q, Tensor k_cache, Tensor v_cache, int G, int Dv, Tensor page_table, Tensor req_slots, Tensor seq_lens, Tensor? cu_q, "
         "int max_q_len, int page_size, float scale, float softcap, int window, Tensor? slopes, Tensor? sinks, Tensor(a!) out, int dim=0, int pad=0) -> ()",
         &window_attention);
+  m.def("attention_sink_gate(Tensor o, Tensor lse, Tensor sinks, int Dv, Tensor(a!) out) -> ()", &attention_sink_gate);
   m.def("moe_softmax_bias_route(Tensor logits, Tensor? corr, int n_real, Tensor(a!) w, Tensor(b!) ids, Tensor(c!) ident) -> ()", &moe_softmax_bias_route);
   m.def("moe_identity_shared_combine(Tensor(a!) y, Tensor h, Tensor? ident, Tensor? shared, Tensor? gate) -> ()", &moe_identity_shared_combine);
   m.def("gated_delta_rule(Tensor u, int Hk, int Dk, int H, int Dv, Tensor a_raw, Tensor A_log, Tensor dt_bias, Tensor b_raw, Tensor(a!) state, "

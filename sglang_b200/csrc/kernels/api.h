@@ -114,6 +114,7 @@ void qk_norm_cache_write(const void* qkv, int ld, bool bf16, int T, int H, int G
 void window_attention(const void* q, const void* kc, const void* vc, bool bf16, size_t ldc, int H, int G, int D, int Dv, const int* page_table,
                       int pt_stride, int page_size, const int* req_slots, const int* seq_lens, const int* cu_q, int B, int max_q_len, float scale,
                       float softcap, int window, const float* slopes, const float* sinks, void* out, int pad, cudaStream_t stream);
+void attention_sink_gate(const void* o, int ldo, const float* lse, const float* sinks, int rows, int H, int Dv, void* out, cudaStream_t stream);
 // mamba.cu (ragged Mamba-2 recurrence), residual_f32.cu (sandwich norms), elementwise.cu (bigram embedding), moe.cu (identity / shared experts)
 void mamba2_scan(const float* u, int ldu, const void* z, int ldz, const void* dt_raw, int lddt, bool bf16, const float* dt_bias, const float* A_log,
                  const float* D, float* state, const int* req_slots, const int* seq_lens, const int* cu_q, int B, int H, int P, int N, int G, float* out,

@@ -290,7 +290,24 @@ void dispatch_wa(const WinAttnParams& p, int B, int max_q_len, cudaStream_t stre
   else launch_wa<T, 8>(p, B, max_q_len, stream);
 }
 
+// out[t, h, :Dv] = o[t, h, :Dv] * sigmoid(lse[t, h] - sink[h]): a sink joins the soft-max denominator of an attention whose kernel returned the
+// log-sum-exp of its scores (exp(lse) / (exp(lse) + exp(sink))); also drops the zero padding behind Dv
+__global__ void __launch_bounds__(128) sink_gate_kernel(const __nv_bfloat16* __restrict__ o, int ldo, const float* __restrict__ lse,
+                                                        const float* __restrict__ sinks, int H, int Dv, __nv_bfloat16* __restrict__ out) {
+  const int row = blockIdx.x;                     // t * H + h
+  const float gte = 1.f / (1.f + expf(sinks[row % H] - lse[row]));
+  const __nv_bfloat16* src = o + (size_t)row * ldo;
+  __nv_bfloat16* dst = out + (size_t)row * Dv;
+  for (int i = threadIdx.x; i < Dv; i += 128) dst[i] = __float2bfloat16(__bfloat162float(src[i]) * gte);
+}
+
 }  // namespace
+
+void attention_sink_gate(const void* o, int ldo, const float* lse, const float* sinks, int rows, int H, int Dv, void* out, cudaStream_t stream) {
+  if (rows <= 0) return;
+  sink_gate_kernel<<<rows, 128, 0, stream>>>((const __nv_bfloat16*)o, ldo, lse, sinks, H, Dv, (__nv_bfloat16*)out);
+  SGLB_CUDA_CHECK(cudaGetLastError());
+}
 
 void qk_norm_cache_write(const void* qkv, int ld, bool bf16, int T, int H, int G, int D, int Dv, const int* positions, float eps, float coef, int every,
                          void* kc, void* vc, size_t ldc, const int* loc, bool normalise, void* q_out, int pad, cudaStream_t stream) {

@@ -107,10 +107,10 @@ class BiasedWindowAttention(nn.Module):
                 o = ops.paged_attention(q, k4, v4, fb.page_table, fb.req_slots, fb.seq_lens, fb.cu_q, fb.q_lens, fb.max_q_len, fb.page_size, self.scale,
                                         causal=True, window=self.window, logit_cap=self.softcap, num_splits=fb.num_splits if dec else 1,
                                         workspace=fb.attn_workspace if dec else None, lse=lse, slopes=self.slopes)
-                if self.Dv < 128:
-                    o = o[:, :, : self.Dv]
                 if lse is not None:
-                    o = (o.float() * torch.sigmoid(lse - self.sinks[None, :]).unsqueeze(-1)).to(o.dtype)
+                    o = ops.attention_sink_gate(o, lse, self.sinks, self.Dv)
+                elif self.Dv < 128:
+                    o = o[:, :, : self.Dv]
                 return ops.linear(o.reshape(T, self.H * self.Dv), self.o_weight)
         o = ops.window_attention(q, kc, vc, self.G, self.Dv, fb.page_table, fb.req_slots, fb.seq_lens, fb.cu_q, fb.q_lens, fb.max_q_len, fb.page_size,
                                  self.scale, self.softcap, self.window, self.slopes, self.sinks, self.D, pad)

@@ -569,6 +569,17 @@ def mamba2_scan(u: torch.Tensor, z: Optional[torch.Tensor], dt_raw: torch.Tensor
     return torch_ref.mamba2_scan(u, z, dt_raw, dt_bias, A_log, D, state, req_slots, seq_lens, q_lens, H, P, N, G)
 
 
+def attention_sink_gate(o: torch.Tensor, lse: torch.Tensor, sinks: torch.Tensor, Dv: Optional[int] = None) -> torch.Tensor:
+    """``o[:, :, :Dv] * sigmoid(lse - sink_h)``: adds a per-head sink to the soft-max denominator of an attention that returned the log-sum-exp
+    of its scores, and drops zero padding behind ``Dv`` (csrc/kernels/window_attention.cu); o [T, H, D] -> [T, H, Dv]"""
+    Dv = o.shape[2] if Dv is None else Dv
+    if _use_native(o) and o.dtype == torch.bfloat16 and o.is_contiguous() and lse.dtype == torch.float32 and lse.is_contiguous():
+        out = torch.empty(o.shape[0], o.shape[1], Dv, dtype=o.dtype, device=o.device)
+        torch.ops.sglb.attention_sink_gate(o, lse, sinks.float().contiguous(), int(Dv), out)
+        return out
+    return (o[:, :, :Dv].float() * torch.sigmoid(lse - sinks[None, :]).unsqueeze(-1)).to(o.dtype)
+
+
 def qk_norm_cache_write(qkv: torch.Tensor, H: int, G: int, D: int, Dv: int, positions: torch.Tensor, eps: float, temp_coef: float, temp_every: int,
                         k_cache: torch.Tensor, v_cache: torch.Tensor, out_cache_loc: torch.Tensor, normalise: bool = True, pad: int = 0) -> torch.Tensor:
     """per-head unit-RMS q and k, position-dependent query temperature, and the write of k / v rows into the paged cache, one kernel

@@ -235,6 +235,7 @@ def test_padded_heads_on_both_attention_routes(H, G, D, Dv, window, cap):
         lse = torch.empty(qb.shape[0], H, dtype=torch.float32, device=DEV)
         o = ops.paged_attention(qb, k4, v4, ptd, _i32(slots), _i32(seq), cu_q, ql, mq, ps, 0.11, True, window, cap, lse=lse, slopes=slopes)
         tc = o[:, :, :Dv].float() * torch.sigmoid(lse - sinks[None, :]).unsqueeze(-1)
+        torch.testing.assert_close(ops.attention_sink_gate(o, lse, sinks, Dv).float(), tc, rtol=1e-2, atol=1e-2)          # the fused form of the line above
         torch.testing.assert_close(tc, plain, rtol=3e-2, atol=3e-2)
         assert (tc - plain).abs().mean().item() < 4e-3
 
