@@ -15,8 +15,9 @@ change, the output's first ``vdim`` columns are the result, and a 64-wide head p
 the CUDA-core kernel (about 3x faster on prompts at that size).  Every other size (heads wider than 128, group sizes that do not divide 128),
 fp32 serving, and any call the tcgen05 kernels do not take stay on the general kernel, which reads the same layout.
 
-The paged pool holds one flat row per token and plane (``cache_width`` columns, the widest layer's ``kv_heads * max(dim, vdim)``): a layer
-reads the first ``kv_heads * dim`` columns of the key plane as its key heads, so layers of different head counts and sizes share one pool.
+The paged pool holds one flat row per token and plane (``cache_width`` columns, the widest layer's ``kv_heads * max(dim, vdim)``, or
+``kv_heads * 128`` for padded layers): a layer reads the first columns of the key plane as its key heads, so layers of different head counts
+and sizes share one pool.
 ``cache_idx`` selects the pool layer: a layer that runs several times per forward owns one pool layer per run.  The window only masks — pages
 behind the window stay with the request until it ends.
 """
