@@ -30,7 +30,7 @@ def _zaparax_cfg(width: int, heads: int, experts: int, top: int, eff: int, share
                                            "q_temp": {"coef": 0.1, "every": 1024}, "scale": 128 ** -0.5, "softcap": 30.0}}
     moe = {"kind": "moe", "expert": {"ff": eff}, "router": {"experts": experts, "identity": 2, "top": top}, "shared": {"ff": shared}}
     return {"architecture": "Zaparax", "width": width, "vocab": 32000, "norm": {"eps": 1e-6},
-            "embedding": {"scale": 1.0, "bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 17}},
+            "embedding": {"scale": 1.0, "bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 13}},
             "layers": [dict(mamba, mlp=moe), dict(attn, mlp=moe), dict(mamba, mlp=moe), dict(attn, mlp=moe)]}
 
 
@@ -220,7 +220,7 @@ def _kernel_numbers(timer: _Timer, hbm_gbs: float, tflops: float) -> List[dict]:
     cu = torch.arange(0, T + 1, 2048, dtype=torch.int32, device=dev)
     slots = torch.arange(4, dtype=torch.int32, device=dev)
     sl = torch.full((4,), 2048, dtype=torch.int32, device=dev)
-    ms = timer(lambda: ops.bigram_embedding(emb, bg, ids, prev, cu, slots, sl, 2048, 1.0, 31, 17, 65521))
+    ms = timer(lambda: ops.bigram_embedding(emb, bg, ids, prev, cu, slots, sl, 2048, 1.0, 31, 13, 65521))
     like = timer(lambda: ops.embedding(emb, ids))
     rec("bigram_embedding", "any", f"T{T} W{Wd} (two rows in, fp32 out: 8 B/elem)", ms, T * Wd * 8, "embedding (one row in, bf16 out: 4 B/elem)", like,
         like_bytes=T * Wd * 4)
